@@ -1,0 +1,184 @@
+// C entry points of the device codec: a handle that owns (or borrows) the look-back workspace and
+// hands out launch epochs.  Counterpart of the per-call cudaMalloc / cudaMemset / 4-byte D2H /
+// cudaFree wrappers of the reference (HomComp/src/GSZ_entry.cu:263-301, :504-550) with none of
+// those on the call path.
+#include <new>
+
+#include "hc_launch.h"
+#include "homcomp_b200.h"
+
+struct hc_codec {
+  void* ws_mem = nullptr;
+  size_t ws_bytes = 0;
+  size_t max_elems = 0;
+  bool owns = false;
+  uint32_t epoch = 0;
+  uint64_t spin_limit_ns = 2000ull * 1000 * 1000;
+};
+
+namespace {
+
+hc::Workspace next_workspace(hc_codec* c, cudaStream_t stream) {
+  c->epoch = (c->epoch + 1) & hc::dev::kEpochMask;
+  if (c->epoch == 0) {
+    // epoch tags wrapped: forget every old status word (2^22 launches apart)
+    cudaMemsetAsync(static_cast<uint8_t*>(c->ws_mem) + 256, 0, c->ws_bytes - 256, stream);
+    c->epoch = 1;
+  }
+  return hc::workspace_view(c->ws_mem, c->max_elems, c->epoch, c->spin_limit_ns);
+}
+
+int check_call(hc_codec* c, size_t n, float eb, bool needs_eb) {
+  if (!c) return hc::kErrArgument;
+  if (n > c->max_elems) return hc::kErrArgument;
+  if (needs_eb && !(eb > 0.0f)) return hc::kErrArgument;
+  return hc::kOk;
+}
+
+int encode_call(hc_codec* c, int op, int mode, const void* local, const uint8_t* in, size_t in_size,
+                const uint8_t* in2, size_t in2_size, size_t n, float eb, uint8_t* out, size_t cap, uint64_t* d_size,
+                cudaStream_t stream) {
+  if (mode < 0 || mode > 2 || !out) return hc::kErrArgument;
+  if (n == 0) {
+    if (d_size) cudaMemsetAsync(d_size, 0, sizeof(uint64_t), stream);
+    return hc::kOk;
+  }
+  hc::EncParams p;
+  memset(&p, 0, sizeof(p));
+  p.local = local;
+  p.n = n;
+  p.recip = 0.5f / eb;
+  p.in = in;
+  p.in_size = in_size;
+  p.in2 = in2;
+  p.in2_size = in2_size;
+  p.n_dst = 1;
+  p.out[0] = out;
+  p.out_cap = cap;
+  p.size_out = d_size;
+  p.ws = next_workspace(c, stream);
+  return hc::launch_encode(op, mode, p, stream) == cudaSuccess ? hc::kOk : hc::kErrCuda;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t hc_codec_workspace_bytes(size_t max_elems) { return hc::workspace_bytes(max_elems); }
+
+int hc_codec_create_in(hc_codec** out, void* d_workspace, size_t bytes, size_t max_elems, hc_stream_t stream) {
+  if (!out || !d_workspace || bytes < hc::workspace_bytes(max_elems)) return hc::kErrArgument;
+  if (reinterpret_cast<uintptr_t>(d_workspace) & 15u) return hc::kErrArgument;
+  hc_codec* c = new (std::nothrow) hc_codec();
+  if (!c) return hc::kErrArgument;
+  c->ws_mem = d_workspace;
+  c->ws_bytes = hc::workspace_bytes(max_elems);
+  c->max_elems = max_elems;
+  if (cudaMemsetAsync(d_workspace, 0, c->ws_bytes, stream) != cudaSuccess) {
+    delete c;
+    return hc::kErrCuda;
+  }
+  *out = c;
+  return hc::kOk;
+}
+
+int hc_codec_create(hc_codec** out, size_t max_elems) {
+  if (!out) return hc::kErrArgument;
+  void* mem = nullptr;
+  size_t bytes = hc::workspace_bytes(max_elems);
+  if (cudaMalloc(&mem, bytes) != cudaSuccess) return hc::kErrCuda;
+  int rc = hc_codec_create_in(out, mem, bytes, max_elems, nullptr);
+  if (rc != hc::kOk) {
+    cudaFree(mem);
+    return rc;
+  }
+  (*out)->owns = true;
+  return hc::kOk;
+}
+
+void hc_codec_destroy(hc_codec* c) {
+  if (!c) return;
+  if (c->owns) cudaFree(c->ws_mem);
+  delete c;
+}
+
+int hc_codec_set_timeout_ms(hc_codec* c, unsigned ms) {
+  if (!c || ms == 0) return hc::kErrArgument;
+  c->spin_limit_ns = (uint64_t)ms * 1000ull * 1000ull;
+  return hc::kOk;
+}
+
+int hc_codec_status(hc_codec* c, int clear) {
+  if (!c) return hc::kErrArgument;
+  uint32_t ctrl[4] = {0, 0, 0, 0};
+  if (cudaDeviceSynchronize() != cudaSuccess) return hc::kErrCuda;
+  if (cudaMemcpy(ctrl, c->ws_mem, sizeof(ctrl), cudaMemcpyDeviceToHost) != cudaSuccess) return hc::kErrCuda;
+  if (clear && (ctrl[2] != 0 || ctrl[0] != 0 || ctrl[1] != 0)) cudaMemset(c->ws_mem, 0, 16);
+  return (int)ctrl[2];
+}
+
+int hc_compress(hc_codec* c, const float* d_x, size_t n, float eb, int mode, uint8_t* d_out, size_t cap,
+                uint64_t* d_size, hc_stream_t stream) {
+  if (int rc = check_call(c, n, eb, true)) return rc;
+  return encode_call(c, hc::kOpCompress, mode, d_x, nullptr, 0, nullptr, 0, n, eb, d_out, cap, d_size, stream);
+}
+
+int hc_hom_add_f32(hc_codec* c, const uint8_t* d_in, size_t in_size, const float* d_local, size_t n, float eb,
+                   int mode, uint8_t* d_out, size_t cap, uint64_t* d_size, hc_stream_t stream) {
+  if (int rc = check_call(c, n, eb, true)) return rc;
+  return encode_call(c, hc::kOpAddF32, mode, d_local, d_in, in_size, nullptr, 0, n, eb, d_out, cap, d_size, stream);
+}
+
+int hc_hom_add_i32(hc_codec* c, const uint8_t* d_in, size_t in_size, const int32_t* d_deltas, size_t n, int mode,
+                   uint8_t* d_out, size_t cap, uint64_t* d_size, hc_stream_t stream) {
+  if (int rc = check_call(c, n, 1.0f, false)) return rc;
+  return encode_call(c, hc::kOpAddI32, mode, d_deltas, d_in, in_size, nullptr, 0, n, 1.0f, d_out, cap, d_size, stream);
+}
+
+int hc_hom_add_stream(hc_codec* c, const uint8_t* d_a, size_t a_size, const uint8_t* d_b, size_t b_size, size_t n,
+                      int mode, uint8_t* d_out, size_t cap, uint64_t* d_size, hc_stream_t stream) {
+  if (int rc = check_call(c, n, 1.0f, false)) return rc;
+  return encode_call(c, hc::kOpAddStream, mode, nullptr, d_a, a_size, d_b, b_size, n, 1.0f, d_out, cap, d_size, stream);
+}
+
+int hc_decompress(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, float eb, int mode, float* d_x,
+                  hc_stream_t stream) {
+  if (int rc = check_call(c, n, eb, true)) return rc;
+  if (mode < 0 || mode > 2 || !d_in || !d_x) return hc::kErrArgument;
+  if (n == 0) return hc::kOk;
+  hc::DecParams p;
+  memset(&p, 0, sizeof(p));
+  p.in = d_in;
+  p.in_size = in_size;
+  p.out = d_x;
+  p.n = n;
+  p.eb = eb;
+  p.ws = next_workspace(c, stream);
+  return hc::launch_decode(mode, p, stream) == cudaSuccess ? hc::kOk : hc::kErrCuda;
+}
+
+int hc_quant_pred(const float* d_x, size_t n, float eb, int mode, int32_t* d_deltas, hc_stream_t stream) {
+  if (!(eb > 0.0f) || !d_x || !d_deltas) return hc::kErrArgument;
+  return hc::launch_quant_pred(mode, d_x, d_deltas, n, eb, stream) == cudaSuccess ? hc::kOk : hc::kErrCuda;
+}
+
+int hc_sum(float* d_dst, const float* d_a, const float* d_b, const float* d_c, const float* d_d, size_t n,
+           hc_stream_t stream) {
+  if (!d_dst || !d_a || !d_b) return hc::kErrArgument;
+  return hc::launch_sum(d_dst, d_a, d_b, d_c, d_d, n, stream) == cudaSuccess ? hc::kOk : hc::kErrCuda;
+}
+
+const char* hc_status_string(int status) {
+  switch (status) {
+    case hc::kOk: return "ok";
+    case hc::kErrCapacity: return "output buffer too small for the stream";
+    case hc::kErrTruncated: return "input stream shorter than its rate bytes imply";
+    case hc::kErrTimeout: return "a bounded device-side wait ran out";
+    case hc::kErrArgument: return "invalid argument";
+    case hc::kErrCuda: return "CUDA runtime error";
+    case hc::kErrPeer: return "a peer failed or never arrived";
+    default: return "unknown status";
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,387 @@
+// The sm_100a codec kernels: one persistent, ticket-ordered kernel family for everything that
+// produces a stream (compress, and the three homomorphic adds) and one for everything that
+// consumes one into fp32 (decompress).
+//
+// Geometry.  A tile is 256 consecutive 32-element blocks (8192 values, 32 KB of fp32); a CTA has
+// 256 threads and thread t owns block t of the tile, i.e. ONE THREAD PER BLOCK with the whole
+// block in registers.  The fp32 tile arrives through a 2-D TMA tiled load ({32, 256} box) with the
+// 128-byte swizzle, which makes the row-per-thread 16-byte shared loads bank-conflict free; the
+// next tile's load is in flight while the current one is processed (two stages, one mbarrier
+// each).  Bit planes come from the in-register transpose of hc_bitplane.h.  The payload of the
+// tile is assembled in shared memory at the same 16-byte phase as its global destination and
+// leaves with 16-byte stores.  Offsets come from a block scan plus a decoupled look-back over
+// 64-bit, epoch-tagged status words, so the workspace is never cleared between launches and the
+// exact stream size lands in device memory (no host round trip).  Tiles are handed out by an
+// atomic ticket, which is what makes the look-back safe under any CTA scheduling.
+//
+// The reference runs one warp per CTA, one thread per 32 blocks with a 4 KB local-memory array per
+// thread, and needs a 4-byte device-to-host copy after every launch
+// (HomComp/src/GSZ.cu:33-756, HomComp/src/GSZ_entry.cu:263-301).
+#pragma once
+#include "hc_bitplane.h"
+#include "hc_device.cuh"
+
+namespace hc {
+
+constexpr int kTileBlocks = 256;
+constexpr int kTileElems = kTileBlocks * kBlock;  // 8192
+constexpr int kTileBytes = kTileElems * 4;        // 32768
+constexpr int kStageBytes = 33 * 1024;            // tile + slack for the 16-byte phase of the stream
+constexpr int kThreads = kTileBlocks;
+constexpr int kMaxDst = 8;
+
+enum Op : int {
+  kOpCompress = 0,   // fp32 -> stream
+  kOpAddF32 = 1,     // stream (+) fp32 -> stream
+  kOpAddI32 = 2,     // stream (+) int32 deltas -> stream
+  kOpAddStream = 3,  // stream (+) stream -> stream
+};
+
+struct Workspace {
+  uint32_t* ctrl;    // [0] ticket, [1] CTAs done, [2] sticky error (hc::Status), [3] spare
+  uint64_t* st_a;    // look-back chain of the first input stream
+  uint64_t* st_b;    // look-back chain of the second input stream
+  uint64_t* st_out;  // look-back chain of the output stream
+  uint32_t epoch;
+  uint64_t spin_limit_ns;
+};
+
+struct EncParams {
+  const void* local;  // fp32 values or int32 deltas of this call
+  uint64_t n;
+  uint32_t n_tiles;
+  uint32_t use_tma;
+  float recip;  // 0.5f / eb
+  const uint8_t* in;
+  uint64_t in_size;
+  const uint8_t* in2;
+  uint64_t in2_size;
+  const uint32_t* in_ready;  // one arrival flag per tile (ring steps), or null
+  uint32_t ring_epoch;
+  uint32_t n_dst;
+  uint8_t* out[kMaxDst];
+  uint32_t* out_ready[kMaxDst];  // arrival flags on the consumers, or null entries
+  uint64_t out_cap;
+  uint64_t* size_out;  // device word receiving the exact stream length (may be null)
+  Workspace ws;
+};
+
+struct DecParams {
+  const uint8_t* in;
+  uint64_t in_size;
+  const uint32_t* in_ready;
+  uint32_t ring_epoch;
+  float* out;
+  uint64_t n;
+  uint32_t n_tiles;
+  uint32_t use_tma;
+  float eb;
+  Workspace ws;
+};
+
+namespace dev {
+
+// ---- per-thread block arithmetic ------------------------------------------------------------
+
+__device__ __forceinline__ int32_t quantise(float x, float recip) {
+  float t = __fmul_rn(x, recip);  // two roundings: the stream is defined without FMA contraction
+  float u = __fadd_rn(t, 0.5f);
+  return __float2int_rz(u) - ((t >= -0.5f) ? 0 : 1);
+}
+
+// 32 values of row `row` from a tile stored with the 128-byte TMA swizzle
+__device__ __forceinline__ void load_row_swizzled(const uint8_t* stage, int row, uint32_t (&w)[32]) {
+  const uint8_t* r = stage + row * 128;
+  const int x = row & 7;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint4 v = *reinterpret_cast<const uint4*>(r + ((c ^ x) << 4));
+    w[4 * c + 0] = v.x; w[4 * c + 1] = v.y; w[4 * c + 2] = v.z; w[4 * c + 3] = v.w;
+  }
+}
+__device__ __forceinline__ void store_row_swizzled(uint8_t* stage, int row, const uint32_t (&w)[32]) {
+  uint8_t* r = stage + row * 128;
+  const int x = row & 7;
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+    *reinterpret_cast<uint4*>(r + ((c ^ x) << 4)) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+}
+
+// plain-load path (unaligned base, tiny inputs) and the ragged last row
+__device__ __forceinline__ void load_row_global(const uint32_t* base, uint64_t n, uint64_t row, uint32_t (&w)[32]) {
+  uint64_t o = row * kBlock;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) w[i] = (o + i < n) ? __ldg(base + o + i) : 0u;
+}
+
+template <int MODE>
+__device__ __forceinline__ void lorenzo_forward(const int32_t (&q)[32], int32_t (&d)[32]) {
+  constexpr int S = MODE == kModeVec ? 4 : 1;
+#pragma unroll
+  for (int i = 31; i >= 0; --i) d[i] = i >= S ? q[i] - q[i - S] : q[i];
+}
+template <int MODE>
+__device__ __forceinline__ void lorenzo_inverse(int32_t (&d)[32]) {
+  constexpr int S = MODE == kModeVec ? 4 : 1;
+#pragma unroll
+  for (int i = S; i < 32; ++i) d[i] += d[i - S];
+}
+
+struct BlockCode {
+  uint32_t rate;      // rate byte
+  uint32_t len;       // payload bytes
+  uint32_t a0;        // |d0| when outlier mode
+  uint32_t sign_mem;  // sign map as the little-endian word that goes to memory
+};
+
+// signed deltas -> rows A[j] = |d[j ^ 7]| plus the block's code
+template <int MODE>
+__device__ __forceinline__ BlockCode analyse_block(const int32_t (&d)[32], uint32_t (&A)[32]) {
+  uint32_t sign = 0, or_all = 0, or_tail = 0;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    uint32_t a = (uint32_t)abs(d[i]);
+    sign = __funnelshift_l((uint32_t)d[i], sign, 1);
+    A[i ^ 7] = a;
+    or_all |= a;
+    if (i) or_tail |= a;
+  }
+  if (or_all & 0x80000000u) {  // INT_MIN deltas: magnitude keeps 31 bits (outside the contract)
+    or_all = 0; or_tail = 0;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      A[i ^ 7] &= 0x7fffffffu;
+      or_all |= A[i ^ 7];
+      if (i) or_tail |= A[i ^ 7];
+    }
+  }
+  BlockCode c;
+  c.a0 = A[7];
+  c.rate = choose_rate(or_all, or_tail, c.a0, MODE != kModePlain);
+  c.len = payload_len(c.rate);
+  c.sign_mem = __byte_perm(sign, 0, 0x0123);
+  if (c.rate & 0x80u) A[7] = 0;
+  return c;
+}
+
+__device__ __forceinline__ void transpose_forward(uint32_t (&A)[32], int W) {
+  switch (W) {
+    case 4: planes_from_rows<4>(A); break;
+    case 8: planes_from_rows<8>(A); break;
+    case 16: planes_from_rows<16>(A); break;
+    case 32: planes_from_rows<32>(A); break;
+    default: break;
+  }
+}
+
+// Writes the block's payload at byte `pos` of the staging buffer.  T holds the planes.
+template <int W>
+__device__ __forceinline__ void write_payload_w(uint8_t* obuf, uint32_t pos, const BlockCode& c, const uint32_t (&T)[32]) {
+  const uint32_t F = c.rate & 31u;
+  const bool outl = (c.rate & 0x80u) != 0;
+  if (!outl && F == 0) return;
+  const uint32_t nout = outl ? ((c.rate >> 5) & 3u) + 1u : 0u;
+#pragma unroll
+  for (uint32_t k = 0; k < 4; ++k)
+    if (k < nout) obuf[pos + k] = (uint8_t)(c.a0 >> (8 * k));
+  const uint32_t p2 = pos + nout;
+  const uint32_t s = p2 & 3u, sh = 8u * s;
+  uint8_t* wb = obuf + (p2 & ~3u);
+  uint32_t prev = 0;
+#pragma unroll
+  for (int j = 0; j <= W + 1; ++j) {
+    uint32_t x;
+    if (j == 0) x = c.sign_mem;
+    else if (j <= W) x = ((uint32_t)(j - 1) < F) ? T[j - 1 < 32 ? j - 1 : 31] : 0u;
+    else x = 0u;
+    uint32_t y = __funnelshift_l(prev, x, sh);
+    if (j == 0) {
+      if (s == 0) *reinterpret_cast<uint32_t*>(wb) = y;
+      else {
+#pragma unroll
+        for (uint32_t b = 1; b < 4; ++b)
+          if (b >= s) wb[b] = (uint8_t)(y >> (8 * b));
+      }
+    } else if ((uint32_t)j <= F) {
+      *reinterpret_cast<uint32_t*>(wb + 4 * j) = y;
+    } else if ((uint32_t)j == F + 1 && s != 0) {
+#pragma unroll
+      for (uint32_t b = 0; b < 3; ++b)
+        if (b < s) wb[4 * j + b] = (uint8_t)(y >> (8 * b));
+    }
+    prev = x;
+  }
+}
+__device__ __forceinline__ void write_payload(uint8_t* obuf, uint32_t pos, const BlockCode& c, const uint32_t (&T)[32],
+                                              int W) {
+  switch (W) {
+    case 0: {  // only "outlier with F = 0" blocks carry bytes here
+      write_payload_w<0>(obuf, pos, c, T);
+      break;
+    }
+    case 4: write_payload_w<4>(obuf, pos, c, T); break;
+    case 8: write_payload_w<8>(obuf, pos, c, T); break;
+    case 16: write_payload_w<16>(obuf, pos, c, T); break;
+    default: write_payload_w<32>(obuf, pos, c, T); break;
+  }
+}
+
+// Reads the block's payload at byte `pos` of a staged stream; returns the sign map (memory form),
+// planes in T[0..W-1] (zero above F) and |d0| of an outlier block in a0.
+template <int W>
+__device__ __forceinline__ void read_payload_w(const uint8_t* cbuf, uint32_t pos, uint32_t rate, uint32_t& sign_mem,
+                                               uint32_t& a0, uint32_t (&T)[32]) {
+  const uint32_t F = rate & 31u;
+  const bool outl = (rate & 0x80u) != 0;
+  const bool has = outl || F != 0;
+  const uint32_t nout = outl ? ((rate >> 5) & 3u) + 1u : 0u;
+  a0 = 0;
+#pragma unroll
+  for (uint32_t k = 0; k < 4; ++k)
+    if (k < nout) a0 |= (uint32_t)cbuf[pos + k] << (8 * k);
+  const uint32_t p2 = pos + nout;
+  const uint32_t sh = 8u * (p2 & 3u);
+  const uint32_t* wp = reinterpret_cast<const uint32_t*>(cbuf + (p2 & ~3u));
+  uint32_t prev = has ? wp[0] : 0u;
+  sign_mem = 0;
+#pragma unroll
+  for (int j = 0; j <= W; ++j) {
+    uint32_t nxt = (has && (uint32_t)j <= F) ? wp[j + 1] : 0u;
+    uint32_t x = __funnelshift_r(prev, nxt, sh);
+    if (j == 0) sign_mem = has ? x : 0u;
+    else T[j - 1 < 32 ? j - 1 : 31] = ((uint32_t)(j - 1) < F) ? x : 0u;
+    prev = nxt;
+  }
+}
+
+// staged payload -> signed deltas d[0..31]
+__device__ __forceinline__ void decode_block(const uint8_t* cbuf, uint32_t pos, uint32_t rate, int W, int32_t (&d)[32]) {
+  uint32_t T[32];
+  uint32_t sign_mem, a0;
+  switch (W) {
+    case 0:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) T[i] = 0;
+      read_payload_w<0>(cbuf, pos, rate, sign_mem, a0, T);
+      break;
+    case 4: read_payload_w<4>(cbuf, pos, rate, sign_mem, a0, T); rows_from_planes<4>(T); break;
+    case 8: read_payload_w<8>(cbuf, pos, rate, sign_mem, a0, T); rows_from_planes<8>(T); break;
+    case 16: read_payload_w<16>(cbuf, pos, rate, sign_mem, a0, T); rows_from_planes<16>(T); break;
+    default: read_payload_w<32>(cbuf, pos, rate, sign_mem, a0, T); rows_from_planes<32>(T); break;
+  }
+  if (rate & 0x80u) T[7] = a0 & 0x7fffffffu;
+  const uint32_t sign = __byte_perm(sign_mem, 0, 0x0123);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    int32_t m = (int32_t)(sign << i) >> 31;
+    d[i] = ((int32_t)T[i ^ 7] ^ m) - m;
+  }
+}
+
+// ---- CTA-wide helpers ------------------------------------------------------------------------
+
+// exclusive scan of one value per thread over the 256-thread CTA; *total = sum.  One barrier.
+__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* s_wsum, uint32_t* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t inc = warp_inclusive_scan(v, lane);
+  if (lane == 31) s_wsum[warp] = inc;
+  __syncthreads();
+  uint32_t pre = 0, tot = 0;
+#pragma unroll
+  for (int w = 0; w < kThreads / 32; ++w) {
+    uint32_t t = s_wsum[w];
+    if (w < warp) pre += t;
+    tot += t;
+  }
+  *total = tot;
+  return inc - v + pre;
+}
+
+__device__ __forceinline__ uint64_t warp_sum_u64(uint64_t v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Decoupled look-back, run by one full warp.  Publishes this tile's aggregate, walks back over
+// the predecessors 32 at a time and returns the exclusive prefix.  *ok = false when a predecessor
+// was poisoned or the bounded wait ran out (then this tile is poisoned too).
+__device__ __forceinline__ uint64_t lookback(uint64_t* st, uint32_t tile, uint32_t epoch, uint64_t agg, uint64_t limit_ns,
+                                             volatile uint32_t* err_word, bool* ok) {
+  const int lane = threadIdx.x & 31;
+  *ok = true;
+  if (tile == 0) {
+    if (lane == 0) st_relaxed_gpu_u64(st, st_pack(kStInc, epoch, agg));
+    return 0;
+  }
+  if (lane == 0) st_relaxed_gpu_u64(st + tile, st_pack(kStAgg, epoch, agg));
+  uint64_t excl = 0;
+  int64_t idx = (int64_t)tile - 1;
+  bool good = true;
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    const int64_t j = idx - lane;
+    uint64_t w = 0;
+    uint32_t s = kStInc;
+    uint32_t it = 0;
+    while (true) {
+      if (j >= 0) {
+        w = ld_relaxed_gpu_u64(st + j);
+        s = st_state(w, epoch);
+      }
+      if (__all_sync(0xffffffffu, s != 0)) break;
+      ++it;
+      bool give_up = false;
+      if ((it & 15u) == 15u) {
+        __nanosleep(40);
+        give_up = (globaltimer_ns() - t0 > limit_ns) || it > (1u << 24) || (*err_word >= (uint32_t)kErrTimeout);
+      }
+      if (__any_sync(0xffffffffu, give_up)) { good = false; break; }
+    }
+    if (!good) break;
+    if (__any_sync(0xffffffffu, s == kStBad)) { good = false; break; }
+    uint64_t v = (j >= 0) ? st_value(w) : 0ull;
+    const uint32_t incmask = __ballot_sync(0xffffffffu, s == kStInc);
+    if (incmask) {
+      const int first = __ffs(incmask) - 1;
+      excl += warp_sum_u64(lane <= first ? v : 0ull);
+      break;
+    }
+    excl += warp_sum_u64(v);
+    idx -= 32;
+  }
+  if (lane == 0) {
+    st_relaxed_gpu_u64(st + tile, st_pack(good ? kStInc : kStBad, epoch, excl + agg));
+    if (!good) atomicMax((uint32_t*)err_word, (uint32_t)kErrTimeout);
+  }
+  *ok = good;
+  return excl;
+}
+
+// bounded wait for an arrival flag written by another GPU
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, uint64_t limit_ns, volatile uint32_t* err_word) {
+  if (ld_acquire_sys_u32(flag) == want) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t it = 0; it < (1u << 26); ++it) {
+    if (ld_acquire_sys_u32(flag) == want) return true;
+    if ((it & 7u) == 7u) {
+      __nanosleep(64);
+      if (globaltimer_ns() - t0 > limit_ns || *err_word >= (uint32_t)kErrTimeout) return false;
+    }
+  }
+  return false;
+}
+
+// copies `bytes` bytes starting at global `src` into `buf` so that buf[phase + k] = src[k], where
+// phase = src & 15 (returned); whole aligned 16-byte units are read, L1 bypassed
+__device__ __forceinline__ uint32_t stage_stream_bytes(uint8_t* buf, const uint8_t* src, uint32_t bytes) {
+  const uint32_t phase = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15u);
+  const uint8_t* al = src - phase;
+  const uint32_t nvec = (phase + bytes + 15u) >> 4;
+  for (uint32_t v = threadIdx.x; v < nvec; v += kThreads)
+    reinterpret_cast<uint4*>(buf)[v] = ld_cg_u4(al + 16ull * v);
+  return phase;
+}
+
+}  // namespace dev
+}  // namespace hc

@@ -1,0 +1,89 @@
+// homcomp-b200: public C API.
+//
+// Layers
+//   hc_cpu_*      portable codec / homomorphic add / host-rank ring (the oracle)
+//   hc_*          sm_100a device codec working on a caller-owned workspace (no allocation, no host
+//                 sync; sizes are produced in device memory)
+//   hc_comm_* / hc_allreduce_*   compressed collectives over peer-mapped buffers
+// The names and signatures of the reference library (GSZ_*, homomorphic_sum*, allreduce_ring_*,
+// cpuCopy_*, mixed_compressed_allreduce) are declared in homcomp_compat.h on top of these.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- format helpers ------------------------------------------------------------------------
+size_t hc_max_compressed_bytes(size_t n);  // capacity that cannot overflow (129 B per block)
+size_t hc_rate_bytes(size_t n);            // length of section A
+
+// mode: 0 outlier codec, 1 plain codec, 2 stride-4 "vec" variant.  All functions return 0 on
+// success or a hc::Status code.
+
+// ---- CPU oracle ----------------------------------------------------------------------------
+int hc_cpu_quantize(const float* x, size_t n, float eb, int32_t* q);
+int hc_cpu_dequantize(const int32_t* q, size_t n, float eb, float* x);
+int hc_cpu_quant_pred(const float* x, size_t n, float eb, int mode, int32_t* deltas);
+int hc_cpu_compress(const float* x, size_t n, float eb, int mode, uint8_t* out, size_t cap, size_t* size);
+int hc_cpu_decompress(const uint8_t* in, size_t size, size_t n, float eb, int mode, float* x);
+int hc_cpu_decode_quant(const uint8_t* in, size_t size, size_t n, int mode, int32_t* q);
+int hc_cpu_hom_add_f32(const uint8_t* in, size_t in_size, const float* local, size_t n, float eb, int mode,
+                       uint8_t* out, size_t cap, size_t* size);
+int hc_cpu_hom_add_i32(const uint8_t* in, size_t in_size, const int32_t* deltas, size_t n, int mode, uint8_t* out,
+                       size_t cap, size_t* size);
+int hc_cpu_hom_add_stream(const uint8_t* a, size_t a_size, const uint8_t* b, size_t b_size, size_t n, int mode,
+                          uint8_t* out, size_t cap, size_t* size);
+int hc_cpu_stream_size(const uint8_t* in, size_t avail, size_t n, size_t* size);
+
+// Ring allreduce of P host buffers simulated in one process (rank r owns bufs[r], `count` floats
+// each).  Results are written to outs[r].  hop_bytes (optional, P*P entries) receives the size of
+// the stream rank r produced at step s as hop_bytes[r*P + s]; step P-1 is the reduced chunk that
+// the all-gather distributes.  Partition and hop order are those of the device ring.
+int hc_cpu_ring_allreduce(const float* const* bufs, float* const* outs, int P, size_t count, float eb,
+                          size_t* hop_bytes);
+// Chunk geometry of the collectives: `count` floats over P ranks, chunk length rounded up to
+// whole 32-element blocks.  Returns the chunk length in elements.
+size_t hc_chunk_elems(size_t count, int P);
+
+// ---- sm_100a device codec -----------------------------------------------------------------------
+// All pointers below are device pointers unless named otherwise.  Calls only enqueue work on
+// `stream`: they never allocate, never synchronise and never copy to the host.  The exact stream
+// length is written to the device word d_size.  One codec handle serialises on one stream at a
+// time (its workspace holds the look-back state of the launch in flight).
+typedef struct CUstream_st* hc_stream_t;  // same type as cudaStream_t
+typedef struct hc_codec hc_codec;
+
+size_t hc_codec_workspace_bytes(size_t max_elems);
+// Workspace owned by the handle (one cudaMalloc here, at set-up time).
+int hc_codec_create(hc_codec** out, size_t max_elems);
+// Workspace provided by the caller (d_workspace of at least hc_codec_workspace_bytes(max_elems));
+// it is zeroed once on `stream`.
+int hc_codec_create_in(hc_codec** out, void* d_workspace, size_t bytes, size_t max_elems, hc_stream_t stream);
+void hc_codec_destroy(hc_codec* c);
+// Upper bound for every device-side wait (look-back, arrival flags, TMA barriers); default 2000 ms.
+int hc_codec_set_timeout_ms(hc_codec* c, unsigned ms);
+// Synchronises the device, returns the sticky hc::Status of the handle and clears it when asked.
+int hc_codec_status(hc_codec* c, int clear);
+
+int hc_compress(hc_codec* c, const float* d_x, size_t n, float eb, int mode, uint8_t* d_out, size_t cap,
+                uint64_t* d_size, hc_stream_t stream);
+int hc_decompress(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, float eb, int mode, float* d_x,
+                  hc_stream_t stream);
+int hc_hom_add_f32(hc_codec* c, const uint8_t* d_in, size_t in_size, const float* d_local, size_t n, float eb,
+                   int mode, uint8_t* d_out, size_t cap, uint64_t* d_size, hc_stream_t stream);
+// d_deltas: hc_quant_pred output, padded to whole 32-element blocks
+int hc_hom_add_i32(hc_codec* c, const uint8_t* d_in, size_t in_size, const int32_t* d_deltas, size_t n, int mode,
+                   uint8_t* d_out, size_t cap, uint64_t* d_size, hc_stream_t stream);
+int hc_hom_add_stream(hc_codec* c, const uint8_t* d_a, size_t a_size, const uint8_t* d_b, size_t b_size, size_t n,
+                      int mode, uint8_t* d_out, size_t cap, uint64_t* d_size, hc_stream_t stream);
+int hc_quant_pred(const float* d_x, size_t n, float eb, int mode, int32_t* d_deltas, hc_stream_t stream);
+// dst = a + b (+ c) (+ d); c and d may be null; dst may alias a
+int hc_sum(float* d_dst, const float* d_a, const float* d_b, const float* d_c, const float* d_d, size_t n,
+           hc_stream_t stream);
+const char* hc_status_string(int status);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,145 @@
+"""sm_100a codec kernels against the CPU oracle: streams must match byte for byte."""
+import numpy as np
+import pytest
+import torch
+
+from tirocinio_triennale_b200 import ops
+from datasets import ALL, SIZES
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def codec():
+    c = ops.Codec(max_elems=1 << 22)
+    yield c
+    assert c.status() == 0
+
+
+def _gpu(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def _stream(out, size):
+    return out[: int(size.item())].cpu().numpy()
+
+
+@pytest.mark.parametrize("name", list(ALL))
+@pytest.mark.parametrize("n", SIZES)
+def test_compress_matches_oracle(codec, name, n):
+    eb = 1e-3
+    x = ALL[name](n, seed=n)
+    out, size = codec.compress(_gpu(x), eb)
+    ref = ops.cpu_compress(x, eb)
+    got = _stream(out, size)
+    assert got.size == ref.size
+    np.testing.assert_array_equal(got, ref)
+    assert codec.status() == 0
+
+
+@pytest.mark.parametrize("mode", ["plain", "vec"])
+@pytest.mark.parametrize("n", [33, 8193, 100000])
+def test_compress_other_modes(codec, mode, n):
+    eb = 1e-4
+    x = ALL["gradient"](n, seed=3)
+    out, size = codec.compress(_gpu(x), eb, mode)
+    np.testing.assert_array_equal(_stream(out, size), ops.cpu_compress(x, eb, mode))
+    y = codec.decompress(out, n, eb, mode)
+    np.testing.assert_array_equal(y.cpu().numpy(), ops.cpu_decompress(ops.cpu_compress(x, eb, mode), n, eb, mode))
+
+
+@pytest.mark.parametrize("name", list(ALL))
+@pytest.mark.parametrize("n", SIZES)
+def test_decompress_matches_oracle(codec, name, n):
+    eb = 1e-3
+    x = ALL[name](n, seed=n + 1)
+    s = ops.cpu_compress(x, eb)
+    pad = np.concatenate([s, np.zeros(32, np.uint8)])
+    y = torch.full((n,), 7.0, device="cuda")  # stale values must be overwritten, zero blocks included
+    codec.decompress(_gpu(pad), n, eb, out=y, stream_bytes=s.size)
+    np.testing.assert_array_equal(y.cpu().numpy(), ops.cpu_decompress(s, n, eb))
+    assert codec.status() == 0
+
+
+@pytest.mark.parametrize("name", list(ALL))
+@pytest.mark.parametrize("n", [1, 33, 8192, 8193, 32769, 262144 + 17])
+def test_hom_add_matches_oracle(codec, name, n):
+    eb = 1e-4 if name != "wide" else 1e-2
+    x, y = ALL[name](n, seed=5), ALL[name](n, seed=6)
+    sx = ops.cpu_compress(x, eb)
+    ref = ops.cpu_hom_add(sx, y, eb)
+    gsx = _gpu(np.concatenate([sx, np.zeros(32, np.uint8)]))
+    out, size = codec.hom_add(gsx, _gpu(y), eb, stream_bytes=sx.size)
+    np.testing.assert_array_equal(_stream(out, size), ref)
+    # two-kernel form: quantise + predict, then add int32 deltas
+    d = codec.quant_pred(_gpu(y), eb)
+    np.testing.assert_array_equal(d.cpu().numpy(), ops.cpu_quant_pred(y, eb))
+    out2, size2 = codec.hom_add_deltas(gsx, d, n, stream_bytes=sx.size)
+    np.testing.assert_array_equal(_stream(out2, size2), ref)
+    # stream (+) stream
+    sy = ops.cpu_compress(y, eb)
+    gsy = _gpu(np.concatenate([sy, np.zeros(32, np.uint8)]))
+    out3, size3 = codec.hom_add_streams(gsx, gsy, n, a_bytes=sx.size, b_bytes=sy.size)
+    np.testing.assert_array_equal(_stream(out3, size3), ref)
+    assert codec.status() == 0
+
+
+def test_unaligned_pointers(codec):
+    n, eb = 20000, 1e-3
+    x = ALL["smooth"](n + 1)
+    gx = _gpu(x)[1:]  # 4-byte aligned only: the plain-load path
+    ref = ops.cpu_compress(x[1:], eb)
+    buf = torch.zeros(ops.max_compressed_bytes(n) + 64, dtype=torch.uint8, device="cuda")
+    out, size = codec.compress(gx.contiguous() if False else gx, eb, out=buf[3:])
+    np.testing.assert_array_equal(out[: int(size.item())].cpu().numpy(), ref)
+    y = torch.zeros(n + 1, device="cuda")
+    codec.decompress(buf[3:], n, eb, out=y[1:], stream_bytes=ref.size)
+    np.testing.assert_array_equal(y[1:].cpu().numpy(), ops.cpu_decompress(ref, n, eb))
+
+
+def test_capacity_and_truncation_are_reported_not_fatal(codec):
+    n, eb = 50000, 1e-4
+    x = ALL["gradient"](n)
+    small = torch.zeros(ops.rate_bytes(n) + 100, dtype=torch.uint8, device="cuda")
+    codec.compress(_gpu(x), eb, out=small)
+    assert codec.status() == 1  # capacity
+    s = ops.cpu_compress(x, eb)
+    y = codec.decompress(_gpu(s), n, eb, stream_bytes=s.size - 1000)
+    assert codec.status() == 2  # truncated
+    assert torch.isfinite(y).all()
+    # the handle keeps working afterwards
+    out, size = codec.compress(_gpu(x), eb)
+    np.testing.assert_array_equal(_stream(out, size), s)
+    assert codec.status() == 0
+
+
+def test_many_launches_reuse_workspace(codec):
+    n, eb = 300000, 1e-4
+    x = ALL["gradient"](n)
+    gx = _gpu(x)
+    ref = ops.cpu_compress(x, eb)
+    for _ in range(50):
+        out, size = codec.compress(gx, eb)
+    np.testing.assert_array_equal(_stream(out, size), ref)
+
+
+def test_large_roundtrip_error_bound(codec):
+    n, eb = (1 << 22) - 5, 1e-4
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(n, device="cuda", generator=g) * 0.01
+    out, size = codec.compress(x, eb)
+    y = codec.decompress(out, n, eb)
+    assert (x - y).abs().max().item() <= eb * 1.001 + 1e-9
+    ratio = 4 * n / int(size.item())
+    assert 1.5 < ratio < 20
+    # against the oracle on the same data
+    np.testing.assert_array_equal(_stream(out, size), ops.cpu_compress(x.cpu().numpy(), eb))
+
+
+def test_sum_kernel(codec):
+    a, b, c, d = (torch.randn(100003, device="cuda") for _ in range(4))
+    dst = torch.empty_like(a)
+    codec.sum(dst, a, b)
+    torch.testing.assert_close(dst, a + b, rtol=0, atol=0)
+    codec.sum(dst, a, b, c, d)
+    torch.testing.assert_close(dst, ((a + b) + c) + d, rtol=0, atol=0)

@@ -1,0 +1,107 @@
+"""Builds the native libraries in-tree.
+
+``libhomcomp_cpu.so``   g++ only: the portable codec, the host-rank ring (the oracle).
+``libhomcomp_b200.so``  nvcc, ``-gencode arch=compute_100a,code=sm_100a``: everything above plus the
+                        sm_100a kernels, the device codec API and the collectives.
+
+The reference builds with a Makefile that passes no ``-arch`` at all (HomComp/src/Makefile:1-4).
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+CSRC = ROOT / "csrc"
+LIBDIR = Path(__file__).resolve().parent / "lib"
+OBJDIR = ROOT / "build" / "obj"
+
+CPU_SOURCES = ["cpu/hc_cpu_codec.cpp", "cpu/hc_cpu_ring.cpp"]
+CUDA_SOURCES = ["cuda/hc_kernels.cu", "cuda/hc_api.cu", "cuda/hc_ring.cu", "cuda/hc_compat.cu", "cuda/hc_noalloc.cu"]
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC,-ffp-contract=off", "--fmad=false",
+]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-ffp-contract=off"]
+
+
+def _existing(sources):
+    return [s for s in sources if (CSRC / s).exists()]
+
+
+def _newest_source_mtime() -> float:
+    m = 0.0
+    for p in CSRC.rglob("*"):
+        if p.suffix in (".cu", ".cuh", ".h", ".cpp"):
+            m = max(m, p.stat().st_mtime)
+    return m
+
+
+def _stale(lib: Path) -> bool:
+    return (not lib.exists()) or lib.stat().st_mtime < _newest_source_mtime()
+
+
+def nvcc_path() -> str | None:
+    for cand in (os.environ.get("HC_NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    return None
+
+
+def _run(cmd):
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("build step failed: %s\n%s\n%s" % (" ".join(map(str, cmd)), r.stdout, r.stderr))
+    return r.stdout + r.stderr
+
+
+def build_cpu(force: bool = False) -> Path:
+    lib = LIBDIR / "libhomcomp_cpu.so"
+    if force or _stale(lib):
+        LIBDIR.mkdir(parents=True, exist_ok=True)
+        tmp = lib.with_suffix(".so.tmp%d" % os.getpid())
+        _run(["g++", *CXX_FLAGS, "-shared", "-I", str(CSRC / "include"),
+              *[str(CSRC / s) for s in CPU_SOURCES], "-o", str(tmp)])
+        os.replace(tmp, lib)
+    return lib
+
+
+def build_cuda(force: bool = False, verbose: bool = False) -> Path:
+    lib = LIBDIR / "libhomcomp_b200.so"
+    if not (force or _stale(lib)):
+        return lib
+    nvcc = nvcc_path()
+    if nvcc is None:
+        raise RuntimeError("nvcc not found; cannot build the sm_100a library")
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    OBJDIR.mkdir(parents=True, exist_ok=True)
+    inc = ["-I", str(CSRC / "include"), "-I", str(CSRC / "cuda")]
+
+    def compile_one(src: str) -> str:
+        obj = OBJDIR / (Path(src).name + ".o")
+        s = CSRC / src
+        if src.endswith(".cu"):
+            extra = ["-Xptxas", "-v"] if verbose else []
+            out = _run([nvcc, *NVCC_FLAGS, *extra, *inc, "-c", str(s), "-o", str(obj)])
+        else:
+            out = _run(["g++", *CXX_FLAGS, *inc, "-c", str(s), "-o", str(obj)])
+        if verbose and out.strip():
+            print(out, file=sys.stderr)
+        return str(obj)
+
+    sources = _existing(CUDA_SOURCES) + CPU_SOURCES
+    with cf.ThreadPoolExecutor(max_workers=min(8, len(sources))) as ex:
+        objs = list(ex.map(compile_one, sources))
+    tmp = lib.with_suffix(".so.tmp%d" % os.getpid())
+    _run([nvcc, "-shared", "-o", str(tmp), *objs, "-lcudart", "-ldl"])
+    os.replace(tmp, lib)
+    return lib
+
+
+if __name__ == "__main__":
+    print(build_cpu(force="--force" in sys.argv))
+    print(build_cuda(force="--force" in sys.argv, verbose="-v" in sys.argv))
