@@ -95,6 +95,7 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
   const uint64_t nrate = rate_bytes(p.n);
   // rows the tensor map covers: int32 deltas come in whole blocks, fp32 data may end in a ragged row
   const uint64_t full_rows = OP == kOpAddI32 ? num_blocks(p.n) : p.n / kBlock;
+  const uint64_t n_local = OP == kOpAddI32 ? num_blocks(p.n) * kBlock : p.n;
 
   if (tid == 0) {
     mbar_init(&sh.mbar[0], 1);
@@ -184,10 +185,11 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) w[i] = 0;
         }
-        // the ragged last row is not part of the tensor map
-        if (row * kBlock < p.n && (row + 1) * kBlock > p.n) load_row_global((const uint32_t*)p.local, p.n, row, w);
+        // the ragged last row of fp32 data is not part of the tensor map
+        if (OP != kOpAddI32 && row * kBlock < p.n && (row + 1) * kBlock > p.n)
+          load_row_global((const uint32_t*)p.local, p.n, row, w);
       } else {
-        load_row_global((const uint32_t*)p.local, p.n, row, w);
+        load_row_global((const uint32_t*)p.local, n_local, row, w);
       }
       int32_t q[32];
       if (OP == kOpAddI32) {
