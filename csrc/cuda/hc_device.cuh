@@ -1,7 +1,7 @@
 // Device-side building blocks for the sm_100a kernels: mbarrier + TMA wrappers, scoped loads and
 // stores, the tile status word of the decoupled look-back, bounded waits.
 //
-// Every wait in this library is bounded: it gives up after `spin_limit_ns` of %globaltimer (or a
+// Every wait in this library is bounded: it gives up after `spin_limit_ns` worth of SM clocks (or a
 // hard iteration cap), records a hc::Status in the workspace's error word and lets the kernel run
 // to its normal end, so a missing peer or a corrupted stream can never hang the GPU.  The reference
 // spins without bound on its look-back flags (HomComp/src/GSZ.cu:204-207).
@@ -45,10 +45,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // bounded wait; false = gave up
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = globaltimer_ns();
+  const long long t0 = clock64();
+  const long long limit_clk = (long long)limit_ns * 2;  // SM clock is at most ~2 GHz
   for (uint32_t it = 0; it < (1u << 26); ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 63u && globaltimer_ns() - t0 > limit_ns) return false;
+    if ((it & 63u) == 63u && clock64() - t0 > limit_clk) return false;
   }
   return false;
 }

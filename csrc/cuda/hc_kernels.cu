@@ -8,17 +8,24 @@
 namespace hc {
 namespace dev {
 
-struct __align__(16) CtaShared {
-  uint64_t mbar[2];
-  uint64_t base_in[2];  // exclusive payload prefix of the tile in input stream 0 / 1
-  uint64_t base_out;
-  int32_t tile[2];
-  uint32_t tile_tma[2];  // 1 when a TMA load was issued for the tile in that stage
-  uint32_t wsum_in[2][kThreads / 32];
-  uint32_t wsum_out[kThreads / 32];
-  uint32_t ok_in[2];
-  uint32_t ok_out;
+constexpr int kEncThreads = kComputeThreads + 64;  // + loader warp + storer warp
+constexpr int kDecThreads = kComputeThreads + 32;  // + loader warp
+constexpr uint32_t kNoTile = 0xffffffffu;
+
+struct __align__(16) EncShared {
+  uint64_t tma_full[2];    // fp32 tile landed in stage s (or "nothing to fetch"); also hands over the ticket
+  uint64_t stage_free[2];  // storer has moved the packed tile out of stage s
+  uint64_t in_full[2];     // input stream bytes + meta staged in buffer b
+  uint64_t in_free[2];     // compute threads have decoded from buffer b
+  uint64_t out_full[2];    // payload of the tile packed in stage s
+  uint32_t tile[4];        // ring of tile tickets, written by the loader
+  uint32_t tile_tma[4];    // 1 when a TMA load was issued for that ring slot
+  uint32_t in_phase[2];    // 16-byte phase of the staged bytes in buffer b
+  uint32_t out_tot[2];     // payload bytes of the tile in stage s
+  uint32_t wsum[2][kComputeThreads / 32];
   uint32_t abort;
+  uint16_t in_rel[2][kTileBlocks];
+  uint8_t in_rate[2][kTileBlocks];
 };
 
 __device__ __forceinline__ void note_error(uint32_t* ctrl, uint32_t code) { atomicMax(ctrl + 2, code); }
@@ -29,6 +36,7 @@ __device__ __forceinline__ bool fatal_error(const uint32_t* ctrl) {
 
 // the last CTA to leave re-arms the ticket counter for the next launch
 __device__ __forceinline__ void cta_epilogue(uint32_t* ctrl) {
+  __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
     uint32_t done = atomicAdd(ctrl + 1, 1u);
@@ -40,56 +48,86 @@ __device__ __forceinline__ void cta_epilogue(uint32_t* ctrl) {
   }
 }
 
-// Stages one input stream's tile: rate byte per thread, block scan, look-back, bytes into `cbuf`.
-// Returns the staged position of this thread's payload (or ~0u when the tile is unusable) and the
-// thread's rate byte.
-__device__ __forceinline__ uint32_t stage_input_tile(const uint8_t* in, uint64_t in_size, uint64_t n, uint32_t tile,
-                                                     uint64_t* st, const Workspace& ws, CtaShared& sh, int which,
-                                                     uint8_t* cbuf, uint32_t* rate_out) {
-  const int tid = threadIdx.x;
-  const uint64_t nrate = rate_bytes(n);
-  uint32_t rate = 0;
-  const uint64_t bidx = (uint64_t)tile * kTileBlocks + tid;
-  if (bidx < in_size) rate = ld_cg_u8(in + bidx);
-  const uint32_t len = payload_len(rate);
-  uint32_t tot;
-  const uint32_t rel = block_exclusive_scan(len, sh.wsum_in[which], &tot);
-  if (tid < 32) {
-    bool ok;
-    uint64_t excl = lookback(st, tile, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
-    if (tid == 0) {
-      sh.base_in[which] = excl;
-      sh.ok_in[which] = ok ? 1u : 0u;
-    }
-  }
-  __syncthreads();
-  const uint64_t base = nrate + sh.base_in[which];
-  bool ok = sh.ok_in[which] != 0;
-  if (ok && base + tot > in_size) {  // stream shorter than its rate bytes imply
-    if (tid == 0) note_error(ws.ctrl, kErrTruncated);
-    ok = false;
-  }
-  uint32_t phase = 0;
-  if (ok && tot) phase = stage_stream_bytes(cbuf, in + base, tot);
-  *rate_out = ok ? rate : 0u;
-  __syncthreads();
-  return phase + rel;
+// bounded mbarrier wait that records a timeout
+__device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, const Workspace& ws, volatile uint32_t* abort) {
+  if (mbar_wait_bounded(bar, parity, ws.spin_limit_ns)) return true;
+  note_error(ws.ctrl, kErrTimeout);
+  *abort = 1;
+  return false;
 }
 
+// Loader-warp work for one input stream: rate bytes -> per-block offsets -> look-back -> one bulk
+// copy of the tile's payload bytes into `cbuf` (16-byte phase preserved).  Arrives on `full`.
+__device__ __forceinline__ void loader_stage_stream(const uint8_t* in, uint64_t in_size, uint64_t nrate, uint32_t tile,
+                                                    uint64_t* st, const Workspace& ws, uint8_t* cbuf, uint64_t* full,
+                                                    uint16_t* s_rel, uint8_t* s_rate, uint32_t* s_phase, bool usable) {
+  const int lane = threadIdx.x & 31;
+  constexpr int kPer = kTileBlocks / 32;  // blocks per lane
+  uint32_t rate[kPer], len[kPer], sum = 0;
+  const uint64_t b0 = (uint64_t)tile * kTileBlocks + (uint64_t)lane * kPer;
+#pragma unroll
+  for (int k = 0; k < kPer; ++k) {
+    rate[k] = (usable && b0 + k < in_size) ? ld_cg_u8(in + b0 + k) : 0u;
+    len[k] = payload_len(rate[k]);
+    sum += len[k];
+  }
+  const uint32_t inc = warp_inclusive_scan(sum, lane);
+  const uint32_t tot = __shfl_sync(0xffffffffu, inc, 31);
+  uint32_t rel = inc - sum;
+#pragma unroll
+  for (int k = 0; k < kPer; ++k) {
+    s_rel[lane * kPer + k] = (uint16_t)rel;
+    rel += len[k];
+  }
+  bool ok;
+  const uint64_t excl = lookback(st, tile, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
+  ok = ok && usable;
+  const uint64_t base = nrate + excl;
+  if (ok && base + tot > in_size) {  // stream shorter than its rate bytes imply
+    if (lane == 0) note_error(ws.ctrl, kErrTruncated);
+    ok = false;
+  }
+#pragma unroll
+  for (int k = 0; k < kPer; ++k) s_rate[lane * kPer + k] = ok ? (uint8_t)rate[k] : (uint8_t)0;
+  const uint8_t* src = in + base;
+  const uint32_t phase = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15u);
+  if (lane == 0) *s_phase = phase;
+  __syncwarp();
+  if (lane == 0) {
+    if (ok && tot) {
+      const uint32_t bytes = (phase + tot + 15u) & ~15u;
+      fence_proxy_async();
+      mbar_expect_tx(full, bytes);
+      bulk_load(cbuf, src - phase, bytes, full);
+    } else {
+      mbar_arrive(full);
+    }
+  }
+}
+
+// Shared-memory plan of the stream-producing kernel (offsets from a 1024-byte aligned base):
+//   [1 KB guard | stage 0 (16 KB) | 1 KB guard | stage 1 (16 KB) | 1 KB guard | cbuf 0 | cbuf 1]
+// A stage first receives the fp32 tile from the TMA unit; once every compute thread holds its row
+// in registers the same bytes become the packing buffer of the tile's payload, which the storer
+// moves out before the loader refills the stage.
+constexpr int kStagePitch = kTileBytes + 1024;
+constexpr int kEncSmemBase = 1024 + 2 * kStagePitch;
+
 template <int OP, int MODE>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kEncThreads, OP == kOpCompress ? 4 : 3)
 hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ CtaShared sh;
+  __shared__ EncShared sh;
   constexpr bool kHasLocal = OP != kOpAddStream;
   constexpr bool kHasIn = OP != kOpCompress;
-  uint8_t* stage[2] = {smem, smem + kStageBytes};
-  uint8_t* cbuf = smem + 2 * kStageBytes;  // staged input stream; later the staged output
-  uint8_t* cbuf2 = smem;                   // second input stream (no local tile in that op)
+  constexpr int kStreams = OP == kOpAddStream ? 2 : (kHasIn ? 1 : 0);
+  uint8_t* stage[2] = {smem + 1024, smem + 1024 + kStagePitch};
+  uint8_t* cbuf[2] = {smem + kEncSmemBase, smem + kEncSmemBase + kBufBytes};
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
+  const int warp = tid >> 5;
   const Workspace& ws = p.ws;
   const bool tma = kHasLocal && p.use_tma;
   const uint64_t nrate = rate_bytes(p.n);
@@ -98,250 +136,308 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
   const uint64_t n_local = OP == kOpAddI32 ? num_blocks(p.n) * kBlock : p.n;
 
   if (tid == 0) {
-    mbar_init(&sh.mbar[0], 1);
-    mbar_init(&sh.mbar[1], 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sh.tma_full[i], 1);
+      mbar_init(&sh.stage_free[i], 1);
+      mbar_init(&sh.in_full[i], 1);
+      mbar_init(&sh.in_free[i], kComputeThreads);
+      mbar_init(&sh.out_full[i], kComputeThreads);
+    }
     fence_mbar_init();
     sh.abort = fatal_error(ws.ctrl) ? 1u : 0u;
-    int32_t t0 = (int32_t)atomicAdd(ws.ctrl, 1u);
-    sh.tile[0] = t0;
-    sh.tile_tma[0] = 0;
-    // a tile that starts past the last full row has nothing to fetch (its rows read as zeros)
-    if (tma && (uint32_t)t0 < p.n_tiles && (uint64_t)t0 * kTileBlocks < full_rows) {
-      mbar_expect_tx(&sh.mbar[0], kTileBytes);
-      tma_load_2d(stage[0], &tmap, 0, t0 * kTileBlocks, &sh.mbar[0]);
-      sh.tile_tma[0] = 1;
-    }
   }
   __syncthreads();
+  volatile uint32_t* abort = &sh.abort;
 
-  uint32_t uses[2] = {0, 0};  // completed TMA loads per stage: the parity to wait for
-  for (uint32_t it = 0;; ++it) {
-    const int cur = it & 1;
-    const uint32_t tile = (uint32_t)sh.tile[cur];
-    if (tile >= p.n_tiles) break;
-    const bool tile_tma = sh.tile_tma[cur] != 0;
-    if (sh.abort) {
-      // a failure somewhere: stop taking work; wait out our own copy in flight first
-      if (tid == 0 && tile_tma) mbar_wait_bounded(&sh.mbar[cur], uses[cur] & 1, ws.spin_limit_ns);
-      break;
-    }
-    if (tid == 0) {
-      int32_t tn = (int32_t)atomicAdd(ws.ctrl, 1u);
-      sh.tile[cur ^ 1] = tn;
-      sh.tile_tma[cur ^ 1] = 0;
-      if (tma && (uint32_t)tn < p.n_tiles && (uint64_t)tn * kTileBlocks < full_rows) {
-        fence_proxy_async();
-        mbar_expect_tx(&sh.mbar[cur ^ 1], kTileBytes);
-        tma_load_2d(stage[cur ^ 1], &tmap, 0, tn * kTileBlocks, &sh.mbar[cur ^ 1]);
-        sh.tile_tma[cur ^ 1] = 1;
-      }
-    }
+  // One input stream: its staging buffer alternates with the tile counter (buffer k & 1, use k >> 1).
+  // Two input streams: stream q owns buffer q (use k).
+  auto in_buf = [&](uint32_t k, int q) -> int { return kStreams == 1 ? (int)(k & 1) : q; };
+  auto in_use = [&](uint32_t k) -> uint32_t { return kStreams == 1 ? (k >> 1) : k; };
 
-    int32_t d[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) d[i] = 0;
-
-    // ---- incoming stream(s) -> signed deltas ------------------------------------------------
-    if (kHasIn) {
-      if (p.in_ready) {
-        if (tid == 0 && !wait_flag(p.in_ready + tile, p.ring_epoch, ws.spin_limit_ns, ws.ctrl + 2)) {
-          note_error(ws.ctrl, kErrPeer);
-          sh.abort = 1;
-        }
-        __syncthreads();
-      }
-      uint32_t rate_in;
-      uint32_t pos = stage_input_tile(p.in, p.in_size, p.n, tile, ws.st_a, ws, sh, 0, cbuf, &rate_in);
-      int W = plane_width(rate_in & 31u);
-      W = __reduce_max_sync(0xffffffffu, W);
-      if (__any_sync(0xffffffffu, rate_in != 0)) decode_block(cbuf, pos, rate_in, W, d);
-      if (OP == kOpAddStream) {
-        uint32_t rate2;
-        uint32_t pos2 = stage_input_tile(p.in2, p.in2_size, p.n, tile, ws.st_b, ws, sh, 1, cbuf2, &rate2);
-        int W2 = plane_width(rate2 & 31u);
-        W2 = __reduce_max_sync(0xffffffffu, W2);
-        if (__any_sync(0xffffffffu, rate2 != 0)) {
-          int32_t d2[32];
-          decode_block(cbuf2, pos2, rate2, W2, d2);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) d[i] += d2[i];
-        }
-      }
-    }
-
-    // ---- local operand -------------------------------------------------------------------------
-    if (kHasLocal) {
-      uint32_t w[32];
-      const uint64_t row = (uint64_t)tile * kTileBlocks + tid;
-      if (tma) {
-        if (tile_tma) {
-          if (!mbar_wait_bounded(&sh.mbar[cur], uses[cur] & 1, ws.spin_limit_ns)) {
-            note_error(ws.ctrl, kErrTimeout);
-            sh.abort = 1;
-          }
-          ++uses[cur];
-          load_row_swizzled(stage[cur], tid, w);  // rows past the map were zero-filled by the TMA unit
+  if (warp == kComputeThreads / 32) {
+    // ================================ loader warp ================================================
+    for (uint32_t k = 0;; ++k) {
+      const int s = k & 1, slot = k & 3;
+      uint32_t tile = kNoTile;
+      if (lane == 0 && !*abort) tile = atomicAdd(ws.ctrl, 1u);
+      tile = __shfl_sync(0xffffffffu, tile, 0);
+      if (tile >= p.n_tiles) tile = kNoTile;
+      // stage s is free once the storer has moved out the tile packed there two turns ago
+      if (k >= 2 && !wait_or_flag(&sh.stage_free[s], ((k >> 1) - 1) & 1, ws, abort)) tile = kNoTile;
+      if (lane == 0) {
+        sh.tile[slot] = tile;
+        const bool fetch = tma && tile != kNoTile && (uint64_t)tile * kTileBlocks < full_rows;
+        sh.tile_tma[slot] = fetch ? 1u : 0u;
+        if (fetch) {
+          fence_proxy_async();
+          mbar_expect_tx(&sh.tma_full[s], kTileBytes);
+          tma_load_2d(stage[s], &tmap, 0, (int)(tile * kTileBlocks), &sh.tma_full[s]);
         } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) w[i] = 0;
+          mbar_arrive(&sh.tma_full[s]);
         }
-        // the ragged last row of fp32 data is not part of the tensor map
-        if (OP != kOpAddI32 && row * kBlock < p.n && (row + 1) * kBlock > p.n)
-          load_row_global((const uint32_t*)p.local, p.n, row, w);
-      } else {
-        load_row_global((const uint32_t*)p.local, n_local, row, w);
       }
-      int32_t q[32];
-      if (OP == kOpAddI32) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) d[i] += (int32_t)w[i];
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) q[i] = quantise(__uint_as_float(w[i]), p.recip);
-        int32_t dl[32];
-        lorenzo_forward<MODE>(q, dl);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) d[i] += dl[i];
-      }
-    }
-
-    // ---- encode ----------------------------------------------------------------------------------
-    uint32_t A[32];
-    BlockCode code = analyse_block<MODE>(d, A);
-    uint32_t tot;
-    const uint32_t rel = block_exclusive_scan(code.len, sh.wsum_out, &tot);  // barrier: inputs are in registers now
-    if (tid < 32) {
-      bool ok;
-      uint64_t excl = lookback(ws.st_out, tile, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
-      if (tid == 0) {
-        sh.base_out = excl;
-        sh.ok_out = ok ? 1u : 0u;
-        if (ok && tile == p.n_tiles - 1 && p.size_out) *p.size_out = nrate + excl + tot;
-      }
-    }
-    int W = plane_width(code.rate & 31u);
-    W = __reduce_max_sync(0xffffffffu, W);
-    transpose_forward(A, W);
-    __syncthreads();
-
-    const uint64_t obase = nrate + sh.base_out;
-    bool ok = sh.ok_out != 0;
-    if (ok && obase + tot > p.out_cap) {
-      if (tid == 0) note_error(ws.ctrl, kErrCapacity);
-      ok = false;
-    }
-    uint8_t* obuf = kHasIn ? cbuf : stage[cur];
-    const uint32_t phase = (uint32_t)((reinterpret_cast<uintptr_t>(p.out[0]) + obase) & 15u);
-    if (ok) write_payload(obuf, phase + rel, code, A, W);
-    __syncthreads();
-    if (ok) {
-      // rate bytes (section A) and payload (section B) to every destination
-      const uint64_t bidx = (uint64_t)tile * kTileBlocks + tid;
-      const uint32_t nvec = (phase + tot + 15u) >> 4;
-      const uint32_t lo_valid = phase, hi_valid = phase + tot;
-#pragma unroll 1
-      for (uint32_t dsti = 0; dsti < p.n_dst; ++dsti) {
-        uint8_t* o = p.out[dsti];
-        o[bidx] = (uint8_t)code.rate;
-        uint8_t* al = o + obase - phase;
-        for (uint32_t v = tid; v < nvec; v += kThreads) {
-          const uint32_t lo = v << 4, hi = lo + 16;
-          if (lo >= lo_valid && hi <= hi_valid) {
-            *reinterpret_cast<uint4*>(al + lo) = reinterpret_cast<const uint4*>(obuf)[v];
-          } else {
-            for (uint32_t b = max(lo, lo_valid); b < min(hi, hi_valid); ++b) al[b] = obuf[b];
+      if (tile == kNoTile) break;
+      if (kHasIn) {
+        bool usable = true;
+        if (p.in_ready) {
+          uint32_t okf = 1;
+          if (lane == 0) okf = wait_flag(p.in_ready + tile, p.ring_epoch, ws.spin_limit_ns, ws.ctrl + 2) ? 1u : 0u;
+          okf = __shfl_sync(0xffffffffu, okf, 0);
+          if (!okf) {
+            if (lane == 0) note_error(ws.ctrl, kErrPeer);
+            usable = false;
           }
         }
+#pragma unroll
+        for (int q = 0; q < kStreams; ++q) {
+          const int b = in_buf(k, q);
+          const uint32_t u = in_use(k);
+          // the buffer is free once the compute threads have decoded its previous tile
+          if (u >= 1 && !wait_or_flag(&sh.in_free[b], (u - 1) & 1, ws, abort)) usable = false;
+          loader_stage_stream(q ? p.in2 : p.in, q ? p.in2_size : p.in_size, nrate, tile, q ? ws.st_b : ws.st_a, ws,
+                              cbuf[b], &sh.in_full[b], sh.in_rel[b], sh.in_rate[b], &sh.in_phase[b], usable);
+        }
       }
     }
-    if (p.out_ready[0] != nullptr) {  // ring step: tell the consumers that this tile has landed
-      __syncthreads();
-      if ((uint32_t)tid < p.n_dst && p.out_ready[tid] != nullptr) {
-        __threadfence_system();
-        st_release_sys_u32(p.out_ready[tid] + tile, ok ? p.ring_epoch : 0xffffffffu);
+  } else if (warp == kComputeThreads / 32 + 1) {
+    // ================================ storer warp ================================================
+    for (uint32_t k = 0;; ++k) {
+      const int s = k & 1;
+      if (!wait_or_flag(&sh.out_full[s], (k >> 1) & 1, ws, abort)) break;
+      const uint32_t tile = sh.tile[k & 3];
+      if (tile == kNoTile) break;
+      const uint32_t tot = sh.out_tot[s];
+      bool ok;
+      const uint64_t excl = lookback(ws.st_out, tile, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
+      const uint64_t goff = nrate + excl;
+      if (ok && goff + tot > p.out_cap) {
+        if (lane == 0) note_error(ws.ctrl, kErrCapacity);
+        ok = false;
       }
+      if (ok) copy_out_warp(stage[s], p.out, p.n_dst, goff, tot, lane);
+      if (ok && lane == 0 && tile == p.n_tiles - 1 && p.size_out) *p.size_out = goff + tot;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh.stage_free[s]);
+      if (p.out_ready[0] != nullptr) {  // a step of a collective: tell the consumers the tile has landed
+        if ((uint32_t)lane < p.n_dst && p.out_ready[lane] != nullptr) {
+          __threadfence_system();
+          st_release_sys_u32(p.out_ready[lane] + tile, ok ? p.ring_epoch : 0xffffffffu);
+        }
+      }
+      if (lane == 0 && fatal_error(ws.ctrl)) *abort = 1;
     }
-    if (tid == 0 && fatal_error(ws.ctrl)) sh.abort = 1;
-    __syncthreads();
+  } else {
+    // ================================ compute warps ==============================================
+    for (uint32_t k = 0;; ++k) {
+      const int s = k & 1, slot = k & 3;
+      bool alive = wait_or_flag(&sh.tma_full[s], (k >> 1) & 1, ws, abort);
+      const uint32_t tile = alive ? sh.tile[slot] : kNoTile;
+      if (tile == kNoTile) {
+        mbar_arrive(&sh.out_full[s]);  // wakes the storer, which sees the end marker too
+        break;
+      }
+      int32_t d[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) d[i] = 0;
+
+      // ---- incoming stream(s) -> signed deltas ------------------------------------------------
+      if (kHasIn) {
+#pragma unroll
+        for (int q = 0; q < kStreams; ++q) {
+          const int b = in_buf(k, q);
+          const bool staged = wait_or_flag(&sh.in_full[b], in_use(k) & 1, ws, abort);
+          const uint32_t rate_in = staged ? sh.in_rate[b][tid] : 0u;
+          const uint32_t pos = sh.in_phase[b] + sh.in_rel[b][tid];
+          int W = plane_width(rate_in & 31u);
+          W = __reduce_max_sync(0xffffffffu, W);
+          if (__any_sync(0xffffffffu, rate_in != 0)) {
+            if (q == 0) {
+              decode_block(cbuf[b], pos, rate_in, W, d);
+            } else {
+              int32_t d2[32];
+              decode_block(cbuf[b], pos, rate_in, W, d2);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) d[i] += d2[i];
+            }
+          }
+          mbar_arrive(&sh.in_free[b]);
+        }
+      }
+
+      // ---- local operand -------------------------------------------------------------------------
+      if (kHasLocal) {
+        uint32_t w[32];
+        const uint64_t row = (uint64_t)tile * kTileBlocks + tid;
+        if (tma) {
+          if (sh.tile_tma[slot]) {
+            load_row_swizzled(stage[s], tid, w);  // rows past the map were zero-filled by the TMA unit
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) w[i] = 0;
+          }
+          // the ragged last row of fp32 data is not part of the tensor map
+          if (OP != kOpAddI32 && row * kBlock < p.n && (row + 1) * kBlock > p.n)
+            load_row_global((const uint32_t*)p.local, p.n, row, w);
+        } else {
+          load_row_global((const uint32_t*)p.local, n_local, row, w);
+        }
+        if (OP == kOpAddI32) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) d[i] += (int32_t)w[i];
+        } else {
+          int32_t q[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) q[i] = quantise(__uint_as_float(w[i]), p.recip);
+          int32_t dl[32];
+          lorenzo_forward<MODE>(q, dl);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) d[i] += dl[i];
+        }
+      }
+
+      // ---- encode ----------------------------------------------------------------------------------
+      uint32_t A[32];
+      BlockCode code = analyse_block<MODE>(d, A);
+      uint32_t tot;
+      // the barrier inside the scan also separates the last read of the fp32 tile from the first
+      // write of the packed payload into the same stage
+      const uint32_t rel = compute_exclusive_scan(code.len, sh.wsum[k & 1], &tot);
+      if (tid == 0) {
+        // publish the tile aggregate right away: successors can look back through this tile
+        if (tile != 0) st_relaxed_gpu_u64(ws.st_out + tile, st_pack(kStAgg, ws.epoch, tot));
+        sh.out_tot[s] = tot;
+      }
+      // rate bytes (section A) go straight to every destination
+      {
+        const uint64_t bidx = (uint64_t)tile * kTileBlocks + tid;
+#pragma unroll 1
+        for (uint32_t dsti = 0; dsti < p.n_dst; ++dsti) p.out[dsti][bidx] = (uint8_t)code.rate;
+      }
+      int W = plane_width(code.rate & 31u);
+      W = __reduce_max_sync(0xffffffffu, W);
+      transpose_forward(A, W);
+      write_payload(stage[s], rel, code, A, W);
+      mbar_arrive(&sh.out_full[s]);
+    }
   }
-  (void)lane;
   cta_epilogue(ws.ctrl);
 }
 
+struct __align__(16) DecShared {
+  uint64_t in_full[2];
+  uint64_t in_free[2];
+  uint32_t tile[4];
+  uint32_t in_phase[2];
+  uint32_t abort;
+  uint16_t in_rel[2][kTileBlocks];
+  uint8_t in_rate[2][kTileBlocks];
+};
+
 template <int MODE>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kDecThreads, 3)
 hc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ CtaShared sh;
+  __shared__ DecShared sh;
   uint8_t* obuf[2] = {smem, smem + kTileBytes};
-  uint8_t* cbuf = smem + 2 * kTileBytes;
+  uint8_t* cbuf[2] = {smem + 2 * kTileBytes, smem + 2 * kTileBytes + kBufBytes};
 
   const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
   const Workspace& ws = p.ws;
   const bool tma = p.use_tma != 0;
   const float eb = p.eb;
-
+  const uint64_t nrate = rate_bytes(p.n);
   const uint64_t full_rows = p.n / kBlock;
+
   if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sh.in_full[i], 1);
+      mbar_init(&sh.in_free[i], kComputeThreads);
+    }
+    fence_mbar_init();
     sh.abort = fatal_error(ws.ctrl) ? 1u : 0u;
-    sh.tile[0] = (int32_t)atomicAdd(ws.ctrl, 1u);
   }
   __syncthreads();
+  volatile uint32_t* abort = &sh.abort;
 
-  for (uint32_t it = 0;; ++it) {
-    const int cur = it & 1;
-    const uint32_t tile = (uint32_t)sh.tile[cur];
-    if (tile >= p.n_tiles) break;
-    if (sh.abort) break;
-    if (tid == 0) {
-      sh.tile[cur ^ 1] = (int32_t)atomicAdd(ws.ctrl, 1u);
-      if (tma) tma_wait_group_read<1>();  // the store that used obuf[cur] two tiles ago has drained
-    }
-    if (p.in_ready) {
-      if (tid == 0 && !wait_flag(p.in_ready + tile, p.ring_epoch, ws.spin_limit_ns, ws.ctrl + 2)) {
-        note_error(ws.ctrl, kErrPeer);
-        sh.abort = 1;
+  if (warp == kComputeThreads / 32) {
+    // ================================ loader warp ================================================
+    for (uint32_t k = 0;; ++k) {
+      const int s = k & 1;
+      uint32_t tile = kNoTile;
+      if (lane == 0 && !*abort) tile = atomicAdd(ws.ctrl, 1u);
+      tile = __shfl_sync(0xffffffffu, tile, 0);
+      if (tile >= p.n_tiles) tile = kNoTile;
+      if (k >= 2 && !wait_or_flag(&sh.in_free[s], ((k >> 1) - 1) & 1, ws, abort)) tile = kNoTile;
+      if (lane == 0) sh.tile[k & 3] = tile;
+      if (tile == kNoTile) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh.in_full[s]);
+        break;
       }
-      __syncthreads();
+      bool usable = true;
+      if (p.in_ready) {
+        uint32_t okf = 1;
+        if (lane == 0) okf = wait_flag(p.in_ready + tile, p.ring_epoch, ws.spin_limit_ns, ws.ctrl + 2) ? 1u : 0u;
+        okf = __shfl_sync(0xffffffffu, okf, 0);
+        if (!okf) {
+          if (lane == 0) note_error(ws.ctrl, kErrPeer);
+          usable = false;
+        }
+      }
+      loader_stage_stream(p.in, p.in_size, nrate, tile, ws.st_a, ws, cbuf[s], &sh.in_full[s], sh.in_rel[s],
+                          sh.in_rate[s], &sh.in_phase[s], usable);
+      if (lane == 0 && fatal_error(ws.ctrl)) *abort = 1;
     }
-    uint32_t rate;
-    uint32_t pos = stage_input_tile(p.in, p.in_size, p.n, tile, ws.st_a, ws, sh, 0, cbuf, &rate);
-    int W = plane_width(rate & 31u);
-    W = __reduce_max_sync(0xffffffffu, W);
-    int32_t d[32];
-    if (__any_sync(0xffffffffu, rate != 0)) {
-      decode_block(cbuf, pos, rate, W, d);
-      lorenzo_inverse<MODE>(d);
-    } else {
+  } else {
+    // ================================ compute warps ==============================================
+    for (uint32_t k = 0;; ++k) {
+      const int s = k & 1;
+      bool alive = wait_or_flag(&sh.in_full[s], (k >> 1) & 1, ws, abort);
+      const uint32_t tile = alive ? sh.tile[k & 3] : kNoTile;
+      if (tile == kNoTile) break;
+      const uint32_t rate = sh.in_rate[s][tid];
+      const uint32_t pos = sh.in_phase[s] + sh.in_rel[s][tid];
+      int W = plane_width(rate & 31u);
+      W = __reduce_max_sync(0xffffffffu, W);
+      int32_t d[32];
+      if (__any_sync(0xffffffffu, rate != 0)) {
+        decode_block(cbuf[s], pos, rate, W, d);
+        lorenzo_inverse<MODE>(d);
+      } else {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) d[i] = 0;
-    }
-    uint32_t w[32];
+        for (int i = 0; i < 32; ++i) d[i] = 0;
+      }
+      mbar_arrive(&sh.in_free[s]);
+      uint32_t w[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(__fmul_rn(__fmul_rn((float)d[i], eb), 2.0f));
+      for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(__fmul_rn(__fmul_rn((float)d[i], eb), 2.0f));
 
-    const uint64_t row = (uint64_t)tile * kTileBlocks + tid;
-    const bool ragged = row * kBlock < p.n && (row + 1) * kBlock > p.n;
-    if (tma) {
-      store_row_swizzled(obuf[cur], tid, w);
-      fence_proxy_async();
-      __syncthreads();
-      if (tid == 0) {
-        if ((uint64_t)tile * kTileBlocks < full_rows) tma_store_2d(&tmap, 0, (int)(tile * kTileBlocks), obuf[cur]);
-        tma_commit_group();  // an empty group keeps the two-deep accounting uniform
+      const uint64_t row = (uint64_t)tile * kTileBlocks + tid;
+      const bool ragged = row * kBlock < p.n && (row + 1) * kBlock > p.n;
+      if (tma) {
+        // the TMA store that used obuf[s] two tiles ago must have finished reading it
+        if (tid == 0) tma_wait_group_read<1>();
+        compute_barrier();
+        store_row_swizzled(obuf[s], tid, w);
+        fence_proxy_async();
+        compute_barrier();
+        if (tid == 0) {
+          if ((uint64_t)tile * kTileBlocks < full_rows) tma_store_2d(&tmap, 0, (int)(tile * kTileBlocks), obuf[s]);
+          tma_commit_group();  // an empty group keeps the two-deep accounting uniform
+        }
+      }
+      if (!tma || ragged) {
+        const uint64_t o = row * kBlock;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (o + i < p.n) p.out[o + i] = __uint_as_float(w[i]);
       }
     }
-    if (!tma || ragged) {
-      const uint64_t o = row * kBlock;
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (o + i < p.n) p.out[o + i] = __uint_as_float(w[i]);
-    }
-    if (tid == 0 && fatal_error(ws.ctrl)) sh.abort = 1;
-    __syncthreads();
+    if (tid == 0 && tma) tma_wait_group<0>();
   }
-  if (tid == 0 && tma) tma_wait_group<0>();
   cta_epilogue(ws.ctrl);
 }
 
@@ -446,9 +542,9 @@ DeviceInfo& device_info() {
   return d;
 }
 
-constexpr int kEncSmemLocalOnly = 2 * kStageBytes + 1024;
-constexpr int kEncSmemWithIn = 3 * kStageBytes + 1024;
-constexpr int kDecSmem = 2 * kTileBytes + kStageBytes + 1024;
+constexpr int kEncSmemLocalOnly = dev::kEncSmemBase + 1024;
+constexpr int kEncSmemWithIn = dev::kEncSmemBase + 2 * kBufBytes + 1024;
+constexpr int kDecSmem = 2 * kTileBytes + 2 * kBufBytes + 1024;
 
 template <typename K>
 cudaError_t set_smem(K kernel, int bytes) {
@@ -466,7 +562,7 @@ cudaError_t launch_encode_t(const CUtensorMap& map, const EncParams& p, int grid
     if (e != cudaSuccess) return e;
     attr_done[dev & 63] = true;
   }
-  dev::hc_encode_kernel<OP, MODE><<<grid, kThreads, smem, stream>>>(map, p);
+  dev::hc_encode_kernel<OP, MODE><<<grid, dev::kEncThreads, smem, stream>>>(map, p);
   return cudaGetLastError();
 }
 
@@ -490,7 +586,7 @@ cudaError_t launch_decode_t(const CUtensorMap& map, const DecParams& p, int grid
     if (e != cudaSuccess) return e;
     attr_done[dev & 63] = true;
   }
-  dev::hc_decode_kernel<MODE><<<grid, kThreads, kDecSmem, stream>>>(map, p);
+  dev::hc_decode_kernel<MODE><<<grid, dev::kDecThreads, kDecSmem, stream>>>(map, p);
   return cudaGetLastError();
 }
 
@@ -531,7 +627,7 @@ cudaError_t launch_encode(int op, int mode, EncParams p, cudaStream_t stream) {
     uint64_t rows = op == kOpAddI32 ? num_blocks(p.n) : p.n / kBlock;
     p.use_tma = make_rows_map(&map, p.local, rows) ? 1u : 0u;
   }
-  int grid = grid_for_tiles(p.n_tiles, 2);
+  int grid = grid_for_tiles(p.n_tiles, op == kOpCompress ? 4 : 3);
   switch (op) {
     case kOpCompress: return launch_encode_m<kOpCompress>(mode, map, p, grid, stream);
     case kOpAddF32: return launch_encode_m<kOpAddF32>(mode, map, p, grid, stream);
@@ -547,7 +643,7 @@ cudaError_t launch_decode(int mode, DecParams p, cudaStream_t stream) {
   CUtensorMap map;
   memset(&map, 0, sizeof(map));
   p.use_tma = make_rows_map(&map, p.out, p.n / kBlock) ? 1u : 0u;
-  int grid = grid_for_tiles(p.n_tiles, 2);
+  int grid = grid_for_tiles(p.n_tiles, 3);
   switch (mode) {
     case kModeOutlier:
     case kModePlain: return launch_decode_t<kModeOutlier>(map, p, grid, stream);

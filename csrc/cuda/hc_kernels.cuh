@@ -1,18 +1,25 @@
-// The sm_100a codec kernels: one persistent, ticket-ordered kernel family for everything that
+// The sm_100a codec kernels: one persistent, warp-specialised kernel family for everything that
 // produces a stream (compress, and the three homomorphic adds) and one for everything that
-// consumes one into fp32 (decompress).
+// consumes a stream into fp32 (decompress).
 //
-// Geometry.  A tile is 256 consecutive 32-element blocks (8192 values, 32 KB of fp32); a CTA has
-// 256 threads and thread t owns block t of the tile, i.e. ONE THREAD PER BLOCK with the whole
-// block in registers.  The fp32 tile arrives through a 2-D TMA tiled load ({32, 256} box) with the
-// 128-byte swizzle, which makes the row-per-thread 16-byte shared loads bank-conflict free; the
-// next tile's load is in flight while the current one is processed (two stages, one mbarrier
-// each).  Bit planes come from the in-register transpose of hc_bitplane.h.  The payload of the
-// tile is assembled in shared memory at the same 16-byte phase as its global destination and
-// leaves with 16-byte stores.  Offsets come from a block scan plus a decoupled look-back over
-// 64-bit, epoch-tagged status words, so the workspace is never cleared between launches and the
-// exact stream size lands in device memory (no host round trip).  Tiles are handed out by an
-// atomic ticket, which is what makes the look-back safe under any CTA scheduling.
+// Geometry.  A tile is 128 consecutive 32-element blocks (4096 values, 16 KB of fp32).  A CTA has
+// four COMPUTE warps in which thread t owns block t of the tile, i.e. one thread per block with
+// the whole block in registers, plus a LOADER warp and a STORER warp:
+//   loader   takes tile tickets, issues the 2-D TMA tiled load of the fp32 tile ({32, 128} box,
+//            128-byte swizzle, two stages), and for the homomorphic adds reads the tile's rate
+//            bytes, scans them, runs the look-back of the INPUT stream and brings the tile's
+//            payload bytes into shared memory with one bulk copy;
+//   compute  decodes the staged payload to deltas, quantises the local values, adds, chooses the
+//            block mode, transposes the magnitudes to bit planes in registers (hc_bitplane.h)
+//            and packs the tile's payload into shared memory;
+//   storer   runs the decoupled look-back of the OUTPUT stream and moves the packed payload to
+//            its byte offset in global (or peer) memory with 16-byte stores, then publishes the
+//            tile's arrival flag when the kernel is a step of a collective.
+// The three roles hand tiles to each other through mbarriers, so the compute warps never wait on
+// a global-memory round trip.  Look-back status words are 64-bit and epoch-tagged: the workspace
+// is never cleared between launches, and the exact stream size lands in device memory (no host
+// round trip).  Tiles are handed out by an atomic ticket, which makes the look-back safe under
+// any CTA scheduling.
 //
 // The reference runs one warp per CTA, one thread per 32 blocks with a 4 KB local-memory array per
 // thread, and needs a 4-byte device-to-host copy after every launch
@@ -23,11 +30,11 @@
 
 namespace hc {
 
-constexpr int kTileBlocks = 256;
-constexpr int kTileElems = kTileBlocks * kBlock;  // 8192
-constexpr int kTileBytes = kTileElems * 4;        // 32768
-constexpr int kStageBytes = 33 * 1024;            // tile + slack for the 16-byte phase of the stream
-constexpr int kThreads = kTileBlocks;
+constexpr int kTileBlocks = 128;
+constexpr int kTileElems = kTileBlocks * kBlock;  // 4096
+constexpr int kTileBytes = kTileElems * 4;        // 16384
+constexpr int kBufBytes = 17 * 1024;              // a tile of stream bytes + alignment slack
+constexpr int kComputeThreads = kTileBlocks;
 constexpr int kMaxDst = 8;
 
 enum Op : int {
@@ -278,17 +285,20 @@ __device__ __forceinline__ void decode_block(const uint8_t* cbuf, uint32_t pos, 
   }
 }
 
-// ---- CTA-wide helpers ------------------------------------------------------------------------
+// ---- cooperative helpers --------------------------------------------------------------------
 
-// exclusive scan of one value per thread over the 256-thread CTA; *total = sum.  One barrier.
-__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* s_wsum, uint32_t* total) {
+__device__ __forceinline__ void compute_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kComputeThreads) : "memory"); }
+
+// exclusive scan of one value per compute thread; *total = sum.  One named barrier; `s_wsum` must
+// not be reused by the next scan before another barrier (callers alternate two arrays).
+__device__ __forceinline__ uint32_t compute_exclusive_scan(uint32_t v, uint32_t* s_wsum, uint32_t* total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   uint32_t inc = warp_inclusive_scan(v, lane);
   if (lane == 31) s_wsum[warp] = inc;
-  __syncthreads();
+  compute_barrier();
   uint32_t pre = 0, tot = 0;
 #pragma unroll
-  for (int w = 0; w < kThreads / 32; ++w) {
+  for (int w = 0; w < kComputeThreads / 32; ++w) {
     uint32_t t = s_wsum[w];
     if (w < warp) pre += t;
     tot += t;
@@ -318,7 +328,8 @@ __device__ __forceinline__ uint64_t lookback(uint64_t* st, uint32_t tile, uint32
   uint64_t excl = 0;
   int64_t idx = (int64_t)tile - 1;
   bool good = true;
-  const uint64_t t0 = globaltimer_ns();
+  const long long t0 = clock64();
+  const long long limit_clk = (long long)limit_ns * 2;  // SM clock is at most ~2 GHz
   while (true) {
     const int64_t j = idx - lane;
     uint64_t w = 0;
@@ -334,7 +345,7 @@ __device__ __forceinline__ uint64_t lookback(uint64_t* st, uint32_t tile, uint32
       bool give_up = false;
       if ((it & 15u) == 15u) {
         __nanosleep(40);
-        give_up = (globaltimer_ns() - t0 > limit_ns) || it > (1u << 24) || (*err_word >= (uint32_t)kErrTimeout);
+        give_up = (clock64() - t0 > limit_clk) || it > (1u << 24) || (*err_word >= (uint32_t)kErrTimeout);
       }
       if (__any_sync(0xffffffffu, give_up)) { good = false; break; }
     }
@@ -361,26 +372,61 @@ __device__ __forceinline__ uint64_t lookback(uint64_t* st, uint32_t tile, uint32
 // bounded wait for an arrival flag written by another GPU
 __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, uint64_t limit_ns, volatile uint32_t* err_word) {
   if (ld_acquire_sys_u32(flag) == want) return true;
-  const uint64_t t0 = globaltimer_ns();
+  const long long t0 = clock64();
+  const long long limit_clk = (long long)limit_ns * 2;
   for (uint32_t it = 0; it < (1u << 26); ++it) {
     if (ld_acquire_sys_u32(flag) == want) return true;
     if ((it & 7u) == 7u) {
       __nanosleep(64);
-      if (globaltimer_ns() - t0 > limit_ns || *err_word >= (uint32_t)kErrTimeout) return false;
+      if (clock64() - t0 > limit_clk || *err_word >= (uint32_t)kErrTimeout) return false;
     }
   }
   return false;
 }
 
-// copies `bytes` bytes starting at global `src` into `buf` so that buf[phase + k] = src[k], where
-// phase = src & 15 (returned); whole aligned 16-byte units are read, L1 bypassed
-__device__ __forceinline__ uint32_t stage_stream_bytes(uint8_t* buf, const uint8_t* src, uint32_t bytes) {
-  const uint32_t phase = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15u);
-  const uint8_t* al = src - phase;
-  const uint32_t nvec = (phase + bytes + 15u) >> 4;
-  for (uint32_t v = threadIdx.x; v < nvec; v += kThreads)
-    reinterpret_cast<uint4*>(buf)[v] = ld_cg_u4(al + 16ull * v);
-  return phase;
+// Moves the `tot` payload bytes packed at obuf[0..tot) to global byte offset `goff` of every
+// destination, with aligned 16-byte stores wherever a whole unit belongs to this tile (run by one
+// warp).  16 readable guard bytes must precede and follow obuf.  All destinations share the same
+// 16-byte phase.
+__device__ __forceinline__ void copy_out_warp(const uint8_t* obuf, uint8_t* const* outs, uint32_t n_dst, uint64_t goff,
+                                              uint32_t tot, int lane) {
+  if (tot == 0) return;
+  const uint32_t phase = (uint32_t)((reinterpret_cast<uintptr_t>(outs[0]) + goff) & 15u);
+  const uint32_t nvec = (phase + tot + 15u) >> 4;
+  const uint32_t sh = ((16u - phase) & 3u) * 8u;
+  const uint32_t lo_valid = phase, hi_valid = phase + tot;
+  for (uint32_t v = lane; v < nvec; v += 32) {
+    const int so = (int)(16u * v) - (int)phase;
+    const uint32_t* wp = reinterpret_cast<const uint32_t*>(obuf + (so & ~3));
+    uint32_t w0 = wp[0], w1 = wp[1], w2 = wp[2], w3 = wp[3], w4 = sh ? wp[4] : 0u;
+    uint32_t o[4] = {__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh), __funnelshift_r(w2, w3, sh),
+                     __funnelshift_r(w3, w4, sh)};
+    const uint32_t lo = 16u * v, hi = lo + 16u;
+    const bool full = lo >= lo_valid && hi <= hi_valid;
+#pragma unroll 1
+    for (uint32_t d = 0; d < n_dst; ++d) {
+      uint8_t* p = outs[d] + goff - phase + lo;
+      if (full) {
+        *reinterpret_cast<uint4*>(p) = make_uint4(o[0], o[1], o[2], o[3]);
+      } else {
+#pragma unroll
+        for (uint32_t b = 0; b < 16; ++b)
+          if (lo + b >= lo_valid && lo + b < hi_valid) p[b] = (uint8_t)(o[b >> 2] >> (8 * (b & 3)));
+      }
+    }
+  }
+}
+
+// 1-D bulk copy global -> shared (TMA unit, no tensor map); both addresses 16-byte aligned, size a
+// multiple of 16
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 }  // namespace dev
