@@ -8,20 +8,24 @@
 namespace hc {
 namespace dev {
 
-constexpr int kEncThreads = kComputeThreads + 64;  // + loader warp + storer warp
+constexpr int kEncThreads = kComputeThreads + 64;  // + loader warp + scanner warp
 constexpr int kDecThreads = kComputeThreads + 32;  // + loader warp
 constexpr uint32_t kNoTile = 0xffffffffu;
 
+constexpr int kMaxStages = 4;
 struct __align__(16) EncShared {
-  uint64_t tma_full[2];    // fp32 tile landed in stage s (or "nothing to fetch"); also hands over the ticket
-  uint64_t stage_free[2];  // storer has moved the packed tile out of stage s
-  uint64_t in_full[2];     // input stream bytes + meta staged in buffer b
-  uint64_t in_free[2];     // compute threads have decoded from buffer b
-  uint64_t out_full[2];    // payload of the tile packed in stage s
-  uint32_t tile[4];        // ring of tile tickets, written by the loader
-  uint32_t tile_tma[4];    // 1 when a TMA load was issued for that ring slot
-  uint32_t in_phase[2];    // 16-byte phase of the staged bytes in buffer b
-  uint32_t out_tot[2];     // payload bytes of the tile in stage s
+  uint64_t tma_full[kMaxStages];    // fp32 tile landed in stage s (or "nothing to fetch"); also hands over the ticket
+  uint64_t stage_free[kMaxStages];  // compute threads have moved the packed tile out of stage s
+  uint64_t scan_done[kMaxStages];   // tile total known: the scanner may start its look-back
+  uint64_t base_ready[kMaxStages];  // look-back of the tile in stage s finished: out_base / out_ok valid
+  uint64_t in_full[2];              // input stream bytes + meta staged in buffer b
+  uint64_t in_free[2];              // compute threads have decoded from buffer b
+  uint32_t tile[8];                 // ring of tile tickets, written by the loader
+  uint32_t tile_tma[8];             // 1 when a TMA load was issued for that ring slot
+  uint32_t in_phase[2];             // 16-byte phase of the staged bytes in buffer b
+  uint32_t out_tot[kMaxStages];     // payload bytes of the tile in stage s
+  uint32_t out_ok[kMaxStages];
+  uint64_t out_base[kMaxStages];    // global byte offset of the tile's payload
   uint32_t wsum[2][kComputeThreads / 32];
   uint32_t abort;
   uint16_t in_rel[2][kTileBlocks];
@@ -59,7 +63,7 @@ __device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, con
 // Loader-warp work for one input stream: rate bytes -> per-block offsets -> look-back -> one bulk
 // copy of the tile's payload bytes into `cbuf` (16-byte phase preserved).  Arrives on `full`.
 __device__ __forceinline__ void loader_stage_stream(const uint8_t* in, uint64_t in_size, uint64_t nrate, uint32_t tile,
-                                                    uint64_t* st, const Workspace& ws, uint8_t* cbuf, uint64_t* full,
+                                                    const Chain& st, const Workspace& ws, uint8_t* cbuf, uint64_t* full,
                                                     uint16_t* s_rel, uint8_t* s_rate, uint32_t* s_phase, bool usable) {
   const int lane = threadIdx.x & 31;
   constexpr int kPer = kTileBlocks / 32;  // blocks per lane
@@ -106,12 +110,14 @@ __device__ __forceinline__ void loader_stage_stream(const uint8_t* in, uint64_t 
 }
 
 // Shared-memory plan of the stream-producing kernel (offsets from a 1024-byte aligned base):
-//   [1 KB guard | stage 0 (16 KB) | 1 KB guard | stage 1 (16 KB) | 1 KB guard | cbuf 0 | cbuf 1]
+//   [1 KB guard | stage 0 (16 KB) | 1 KB guard | ... | stage NS-1 | 1 KB guard | cbuf 0 | cbuf 1]
 // A stage first receives the fp32 tile from the TMA unit; once every compute thread holds its row
-// in registers the same bytes become the packing buffer of the tile's payload, which the storer
-// moves out before the loader refills the stage.
+// in registers the same bytes become the packing buffer of the tile's payload, which leaves
+// moves out before the loader refills the stage.  NS = 3 when nothing else needs shared memory
+// (compress: 4 CTAs per SM), 2 when an input stream is staged too (3 CTAs per SM).
 constexpr int kStagePitch = kTileBytes + 1024;
-constexpr int kEncSmemBase = 1024 + 2 * kStagePitch;
+__host__ __device__ constexpr int enc_stages(int op) { return op == kOpCompress ? 3 : 2; }
+__host__ __device__ constexpr int enc_smem_base(int op) { return 1024 + enc_stages(op) * kStagePitch; }
 
 template <int OP, int MODE>
 __global__ void __launch_bounds__(kEncThreads, OP == kOpCompress ? 4 : 3)
@@ -122,8 +128,9 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
   constexpr bool kHasLocal = OP != kOpAddStream;
   constexpr bool kHasIn = OP != kOpCompress;
   constexpr int kStreams = OP == kOpAddStream ? 2 : (kHasIn ? 1 : 0);
-  uint8_t* stage[2] = {smem + 1024, smem + 1024 + kStagePitch};
-  uint8_t* cbuf[2] = {smem + kEncSmemBase, smem + kEncSmemBase + kBufBytes};
+  constexpr int NS = enc_stages(OP);
+  uint8_t* const stage0 = smem + 1024;
+  uint8_t* cbuf[2] = {smem + enc_smem_base(OP), smem + enc_smem_base(OP) + kBufBytes};
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -136,18 +143,40 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
   const uint64_t n_local = OP == kOpAddI32 ? num_blocks(p.n) * kBlock : p.n;
 
   if (tid == 0) {
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(&sh.tma_full[i], 1);
-      mbar_init(&sh.stage_free[i], 1);
+      mbar_init(&sh.stage_free[i], kComputeThreads);
+      mbar_init(&sh.scan_done[i], 1);
+      mbar_init(&sh.base_ready[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&sh.in_full[i], 1);
       mbar_init(&sh.in_free[i], kComputeThreads);
-      mbar_init(&sh.out_full[i], kComputeThreads);
     }
     fence_mbar_init();
     sh.abort = fatal_error(ws.ctrl) ? 1u : 0u;
   }
   __syncthreads();
   volatile uint32_t* abort = &sh.abort;
+
+  // The packed payload leaves one tile late when there are three stages (its look-back has a whole
+  // tile time to finish), and in the same turn when there are two.
+  constexpr int kLag = NS >= 3 ? 1 : 0;
+  auto move_out = [&](uint32_t j) {  // compute threads: tile number j of this CTA -> global memory
+    const int sj = j % NS;
+    wait_or_flag(&sh.base_ready[sj], (j / NS) & 1, ws, abort);
+    const uint32_t tile = sh.tile[j & 7];
+    const bool ok = sh.out_ok[sj] != 0;
+    if (ok) copy_out(stage0 + sj * kStagePitch, p.out, p.n_dst, sh.out_base[sj], sh.out_tot[sj], tid, kComputeThreads);
+    if (p.out_ready[0] != nullptr) {  // a step of a collective: tell the consumers the tile has landed
+      compute_barrier();
+      if ((uint32_t)tid < p.n_dst && p.out_ready[tid] != nullptr) {
+        __threadfence_system();
+        st_release_sys_u32(p.out_ready[tid] + tile, ok ? p.ring_epoch : 0xffffffffu);
+      }
+    }
+    mbar_arrive(&sh.stage_free[sj]);
+  };
 
   // One input stream: its staging buffer alternates with the tile counter (buffer k & 1, use k >> 1).
   // Two input streams: stream q owns buffer q (use k).
@@ -156,14 +185,16 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
 
   if (warp == kComputeThreads / 32) {
     // ================================ loader warp ================================================
+    // tickets are taken one turn ahead so the atomic's round trip is off the refill path
+    uint32_t next_tile = kNoTile;
+    if (lane == 0 && !*abort) next_tile = atomicAdd(ws.ctrl, 1u);
     for (uint32_t k = 0;; ++k) {
-      const int s = k & 1, slot = k & 3;
-      uint32_t tile = kNoTile;
-      if (lane == 0 && !*abort) tile = atomicAdd(ws.ctrl, 1u);
-      tile = __shfl_sync(0xffffffffu, tile, 0);
+      const int s = k % NS, slot = k & 7;
+      uint32_t tile = __shfl_sync(0xffffffffu, next_tile, 0);
       if (tile >= p.n_tiles) tile = kNoTile;
-      // stage s is free once the storer has moved out the tile packed there two turns ago
-      if (k >= 2 && !wait_or_flag(&sh.stage_free[s], ((k >> 1) - 1) & 1, ws, abort)) tile = kNoTile;
+      if (tile != kNoTile && lane == 0) next_tile = *abort ? kNoTile : atomicAdd(ws.ctrl, 1u);
+      // stage s is free once the tile packed there NS turns ago has been moved out
+      if (k >= NS && !wait_or_flag(&sh.stage_free[s], ((k / NS) - 1) & 1, ws, abort)) tile = kNoTile;
       if (lane == 0) {
         sh.tile[slot] = tile;
         const bool fetch = tma && tile != kNoTile && (uint64_t)tile * kTileBlocks < full_rows;
@@ -171,7 +202,7 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
         if (fetch) {
           fence_proxy_async();
           mbar_expect_tx(&sh.tma_full[s], kTileBytes);
-          tma_load_2d(stage[s], &tmap, 0, (int)(tile * kTileBlocks), &sh.tma_full[s]);
+          tma_load_2d(stage0 + s * kStagePitch, &tmap, 0, (int)(tile * kTileBlocks), &sh.tma_full[s]);
         } else {
           mbar_arrive(&sh.tma_full[s]);
         }
@@ -194,46 +225,50 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
           const uint32_t u = in_use(k);
           // the buffer is free once the compute threads have decoded its previous tile
           if (u >= 1 && !wait_or_flag(&sh.in_free[b], (u - 1) & 1, ws, abort)) usable = false;
-          loader_stage_stream(q ? p.in2 : p.in, q ? p.in2_size : p.in_size, nrate, tile, q ? ws.st_b : ws.st_a, ws,
+          loader_stage_stream(q ? p.in2 : p.in, q ? p.in2_size : p.in_size, nrate, tile, q ? Chain{ws.st_b, ws.grp_b} : Chain{ws.st_a, ws.grp_a}, ws,
                               cbuf[b], &sh.in_full[b], sh.in_rel[b], sh.in_rate[b], &sh.in_phase[b], usable);
         }
       }
     }
   } else if (warp == kComputeThreads / 32 + 1) {
-    // ================================ storer warp ================================================
+    // ================================ scanner warp ===============================================
+    // runs the decoupled look-back of the output stream as soon as a tile's total is known, while
+    // the compute warps are still transposing and packing; hands them the tile's global offset
     for (uint32_t k = 0;; ++k) {
-      const int s = k & 1;
-      if (!wait_or_flag(&sh.out_full[s], (k >> 1) & 1, ws, abort)) break;
-      const uint32_t tile = sh.tile[k & 3];
+      const int s = k % NS;
+      const uint32_t par = (k / NS) & 1;
+      if (!wait_or_flag(&sh.scan_done[s], par, ws, abort)) break;
+      const uint32_t tile = sh.tile[k & 7];
       if (tile == kNoTile) break;
       const uint32_t tot = sh.out_tot[s];
-      bool ok;
-      const uint64_t excl = lookback(ws.st_out, tile, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
+      bool ok = true;
+      const uint64_t excl = lookback(Chain{ws.st_out, ws.grp_out}, tile, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
       const uint64_t goff = nrate + excl;
       if (ok && goff + tot > p.out_cap) {
         if (lane == 0) note_error(ws.ctrl, kErrCapacity);
         ok = false;
       }
-      if (ok) copy_out_warp(stage[s], p.out, p.n_dst, goff, tot, lane);
-      if (ok && lane == 0 && tile == p.n_tiles - 1 && p.size_out) *p.size_out = goff + tot;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh.stage_free[s]);
-      if (p.out_ready[0] != nullptr) {  // a step of a collective: tell the consumers the tile has landed
-        if ((uint32_t)lane < p.n_dst && p.out_ready[lane] != nullptr) {
-          __threadfence_system();
-          st_release_sys_u32(p.out_ready[lane] + tile, ok ? p.ring_epoch : 0xffffffffu);
-        }
+      if (lane == 0) {
+        sh.out_base[s] = goff;
+        sh.out_ok[s] = ok ? 1u : 0u;
+        mbar_arrive(&sh.base_ready[s]);
+        if (ok && tile == p.n_tiles - 1 && p.size_out) *p.size_out = goff + tot;
+        if (fatal_error(ws.ctrl)) *abort = 1;
       }
-      if (lane == 0 && fatal_error(ws.ctrl)) *abort = 1;
     }
   } else {
     // ================================ compute warps ==============================================
     for (uint32_t k = 0;; ++k) {
-      const int s = k & 1, slot = k & 3;
-      bool alive = wait_or_flag(&sh.tma_full[s], (k >> 1) & 1, ws, abort);
+      const int s = k % NS, slot = k & 7;
+      uint8_t* const stage_s = stage0 + s * kStagePitch;
+      bool alive = wait_or_flag(&sh.tma_full[s], (k / NS) & 1, ws, abort);
       const uint32_t tile = alive ? sh.tile[slot] : kNoTile;
       if (tile == kNoTile) {
-        mbar_arrive(&sh.out_full[s]);  // wakes the storer, which sees the end marker too
+        if (kLag && k >= 1) {
+          compute_barrier();  // no scan barrier this turn: wait until every thread has packed
+          move_out(k - 1);
+        }
+        if (tid == 0) mbar_arrive(&sh.scan_done[s]);  // wakes the scanner, which sees the end marker too
         break;
       }
       int32_t d[32];
@@ -270,7 +305,7 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
         const uint64_t row = (uint64_t)tile * kTileBlocks + tid;
         if (tma) {
           if (sh.tile_tma[slot]) {
-            load_row_swizzled(stage[s], tid, w);  // rows past the map were zero-filled by the TMA unit
+            load_row_swizzled(stage_s, tid, w);  // rows past the map were zero-filled by the TMA unit
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) w[i] = 0;
@@ -306,6 +341,7 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
         // publish the tile aggregate right away: successors can look back through this tile
         if (tile != 0) st_relaxed_gpu_u64(ws.st_out + tile, st_pack(kStAgg, ws.epoch, tot));
         sh.out_tot[s] = tot;
+        mbar_arrive(&sh.scan_done[s]);
       }
       // rate bytes (section A) go straight to every destination
       {
@@ -316,8 +352,13 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
       int W = plane_width(code.rate & 31u);
       W = __reduce_max_sync(0xffffffffu, W);
       transpose_forward(A, W);
-      write_payload(stage[s], rel, code, A, W);
-      mbar_arrive(&sh.out_full[s]);
+      write_payload(stage_s, rel, code, A, W);
+      if (kLag == 0) {
+        compute_barrier();  // every thread's payload is packed
+        move_out(k);
+      } else if (k >= 1) {
+        move_out(k - 1);  // packed before this turn's scan barrier
+      }
     }
   }
   cta_epilogue(ws.ctrl);
@@ -387,7 +428,7 @@ hc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecParams p) {
           usable = false;
         }
       }
-      loader_stage_stream(p.in, p.in_size, nrate, tile, ws.st_a, ws, cbuf[s], &sh.in_full[s], sh.in_rel[s],
+      loader_stage_stream(p.in, p.in_size, nrate, tile, Chain{ws.st_a, ws.grp_a}, ws, cbuf[s], &sh.in_full[s], sh.in_rel[s],
                           sh.in_rate[s], &sh.in_phase[s], usable);
       if (lane == 0 && fatal_error(ws.ctrl)) *abort = 1;
     }
@@ -542,8 +583,8 @@ DeviceInfo& device_info() {
   return d;
 }
 
-constexpr int kEncSmemLocalOnly = dev::kEncSmemBase + 1024;
-constexpr int kEncSmemWithIn = dev::kEncSmemBase + 2 * kBufBytes + 1024;
+constexpr int kEncSmemLocalOnly = dev::enc_smem_base(kOpCompress) + 1024;
+constexpr int kEncSmemWithIn = dev::enc_smem_base(kOpAddF32) + 2 * kBufBytes + 1024;
 constexpr int kDecSmem = 2 * kTileBytes + 2 * kBufBytes + 1024;
 
 template <typename K>
@@ -594,7 +635,8 @@ cudaError_t launch_decode_t(const CUtensorMap& map, const DecParams& p, int grid
 
 size_t workspace_bytes(size_t max_elems) {
   size_t tiles = rate_bytes(max_elems) / kTileBlocks + 1;
-  return 256 + 3 * tiles * sizeof(uint64_t);
+  size_t groups = tiles / 32 + 1;
+  return 256 + 3 * (tiles + groups) * sizeof(uint64_t);
 }
 
 Workspace workspace_view(void* mem, size_t max_elems, uint32_t epoch, uint64_t spin_limit_ns) {
@@ -602,9 +644,13 @@ Workspace workspace_view(void* mem, size_t max_elems, uint32_t epoch, uint64_t s
   Workspace w;
   uint8_t* b = static_cast<uint8_t*>(mem);
   w.ctrl = reinterpret_cast<uint32_t*>(b);
+  size_t groups = tiles / 32 + 1;
   w.st_a = reinterpret_cast<uint64_t*>(b + 256);
   w.st_b = w.st_a + tiles;
   w.st_out = w.st_b + tiles;
+  w.grp_a = w.st_out + tiles;
+  w.grp_b = w.grp_a + groups;
+  w.grp_out = w.grp_b + groups;
   w.epoch = epoch;
   w.spin_limit_ns = spin_limit_ns;
   return w;

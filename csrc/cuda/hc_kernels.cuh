@@ -46,9 +46,12 @@ enum Op : int {
 
 struct Workspace {
   uint32_t* ctrl;    // [0] ticket, [1] CTAs done, [2] sticky error (hc::Status), [3] spare
-  uint64_t* st_a;    // look-back chain of the first input stream
+  uint64_t* st_a;    // look-back chain of the first input stream (tile words, then group words)
   uint64_t* st_b;    // look-back chain of the second input stream
   uint64_t* st_out;  // look-back chain of the output stream
+  uint64_t* grp_a;
+  uint64_t* grp_b;
+  uint64_t* grp_out;
   uint32_t epoch;
   uint64_t spin_limit_ns;
 };
@@ -144,23 +147,24 @@ struct BlockCode {
 // signed deltas -> rows A[j] = |d[j ^ 7]| plus the block's code
 template <int MODE>
 __device__ __forceinline__ BlockCode analyse_block(const int32_t (&d)[32], uint32_t (&A)[32]) {
-  uint32_t sign = 0, or_all = 0, or_tail = 0;
+  uint32_t sign = 0, or_tail = 0;
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
-    uint32_t a = (uint32_t)abs(d[i]);
+    A[i ^ 7] = (uint32_t)abs(d[i]);
     sign = __funnelshift_l((uint32_t)d[i], sign, 1);
-    A[i ^ 7] = a;
-    or_all |= a;
-    if (i) or_tail |= a;
   }
+#pragma unroll
+  for (int i = 1; i < 31; i += 2) or_tail |= A[i ^ 7] | A[(i + 1) ^ 7];  // one 3-input LOP3 per pair
+  or_tail |= A[31 ^ 7];
+  uint32_t or_all = or_tail | A[7];
   if (or_all & 0x80000000u) {  // INT_MIN deltas: magnitude keeps 31 bits (outside the contract)
-    or_all = 0; or_tail = 0;
+    or_tail = 0;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       A[i ^ 7] &= 0x7fffffffu;
-      or_all |= A[i ^ 7];
       if (i) or_tail |= A[i ^ 7];
     }
+    or_all = or_tail | A[7];
   }
   BlockCode c;
   c.a0 = A[7];
@@ -181,42 +185,48 @@ __device__ __forceinline__ void transpose_forward(uint32_t (&A)[32], int W) {
   }
 }
 
-// Writes the block's payload at byte `pos` of the staging buffer.  T holds the planes.
+// Writes the block's payload at byte `pos` of the staging buffer.  T[0..W-1] hold the planes
+// (planes at and above F are zero because every magnitude is below 2^F).
 template <int W>
 __device__ __forceinline__ void write_payload_w(uint8_t* obuf, uint32_t pos, const BlockCode& c, const uint32_t (&T)[32]) {
   const uint32_t F = c.rate & 31u;
   const bool outl = (c.rate & 0x80u) != 0;
   if (!outl && F == 0) return;
-  const uint32_t nout = outl ? ((c.rate >> 5) & 3u) + 1u : 0u;
+  uint32_t p2 = pos;
+  if (outl) {
+    const uint32_t nout = ((c.rate >> 5) & 3u) + 1u;
 #pragma unroll
-  for (uint32_t k = 0; k < 4; ++k)
-    if (k < nout) obuf[pos + k] = (uint8_t)(c.a0 >> (8 * k));
-  const uint32_t p2 = pos + nout;
-  const uint32_t s = p2 & 3u, sh = 8u * s;
-  uint8_t* wb = obuf + (p2 & ~3u);
-  uint32_t prev = 0;
+    for (uint32_t k = 0; k < 4; ++k)
+      if (k < nout) obuf[pos + k] = (uint8_t)(c.a0 >> (8 * k));
+    p2 += nout;
+  }
+  const uint32_t s = p2 & 3u;
+  if (s == 0) {  // word-aligned block: plain predicated word stores
+    uint32_t* wp = reinterpret_cast<uint32_t*>(obuf + p2);
+    wp[0] = c.sign_mem;
 #pragma unroll
-  for (int j = 0; j <= W + 1; ++j) {
-    uint32_t x;
-    if (j == 0) x = c.sign_mem;
-    else if (j <= W) x = ((uint32_t)(j - 1) < F) ? T[j - 1 < 32 ? j - 1 : 31] : 0u;
-    else x = 0u;
-    uint32_t y = __funnelshift_l(prev, x, sh);
-    if (j == 0) {
-      if (s == 0) *reinterpret_cast<uint32_t*>(wb) = y;
-      else {
+    for (int j = 1; j <= W; ++j)
+      if ((uint32_t)j <= F) wp[j] = T[j - 1];
+  } else {  // shifted block: every aligned word takes bytes of two neighbours
+    const uint32_t sh = 8u * s;
+    uint8_t* wb = obuf + (p2 & ~3u);
+    uint32_t prev = c.sign_mem;
+    const uint32_t head = prev << sh;
 #pragma unroll
-        for (uint32_t b = 1; b < 4; ++b)
-          if (b >= s) wb[b] = (uint8_t)(y >> (8 * b));
-      }
-    } else if ((uint32_t)j <= F) {
-      *reinterpret_cast<uint32_t*>(wb + 4 * j) = y;
-    } else if ((uint32_t)j == F + 1 && s != 0) {
+    for (uint32_t b = 1; b < 4; ++b)
+      if (b >= s) wb[b] = (uint8_t)(head >> (8 * b));
 #pragma unroll
-      for (uint32_t b = 0; b < 3; ++b)
-        if (b < s) wb[4 * j + b] = (uint8_t)(y >> (8 * b));
+    for (int j = 1; j <= W; ++j) {
+      const uint32_t x = T[j - 1];
+      const bool live = (uint32_t)j <= F;
+      if (live) *reinterpret_cast<uint32_t*>(wb + 4 * j) = __funnelshift_l(prev, x, sh);
+      prev = live ? x : prev;
     }
-    prev = x;
+    const uint32_t tail = prev >> (32u - sh);  // the last word's upper bytes spill into the next aligned word
+    uint8_t* tb = wb + 4 * (F + 1);
+#pragma unroll
+    for (uint32_t b = 0; b < 3; ++b)
+      if (b < s) tb[b] = (uint8_t)(tail >> (8 * b));
   }
 }
 __device__ __forceinline__ void write_payload(uint8_t* obuf, uint32_t pos, const BlockCode& c, const uint32_t (&T)[32],
@@ -313,56 +323,112 @@ __device__ __forceinline__ uint64_t warp_sum_u64(uint64_t v) {
   return v;
 }
 
-// Decoupled look-back, run by one full warp.  Publishes this tile's aggregate, walks back over
-// the predecessors 32 at a time and returns the exclusive prefix.  *ok = false when a predecessor
-// was poisoned or the bounded wait ran out (then this tile is poisoned too).
-__device__ __forceinline__ uint64_t lookback(uint64_t* st, uint32_t tile, uint32_t epoch, uint64_t agg, uint64_t limit_ns,
-                                             volatile uint32_t* err_word, bool* ok) {
+// Two-level decoupled look-back, run by one full warp.
+//
+// Level 1: status word per tile.  Level 2: status word per GROUP of 32 tiles, published by the
+// group's last tile (aggregate of the group as soon as its 32 tile aggregates are known, inclusive
+// prefix once that tile has resolved its own).  A tile first sums the aggregates of the earlier
+// tiles of its own group (one 32-wide poll), then walks back over whole groups, 32 groups = 1024
+// tiles per poll.  With hundreds of tiles in flight a one-level walk needs (tiles in flight / 64)
+// dependent polls per wave; this needs two or three.
+//
+// Publishes this tile's aggregate first and returns the exclusive prefix.  *ok = false when a
+// predecessor was poisoned or the bounded wait ran out (then this tile is poisoned too).
+struct Chain {
+  uint64_t* tile_st;   // one word per tile
+  uint64_t* group_st;  // one word per 32 tiles
+};
+
+// One 32-wide look at `st[idx], st[idx-1], ...` (lane l looks at idx - l; indices below `lo` count
+// as "inclusive 0").  Consumes the longest ready run starting at idx.  Returns the number of
+// entries consumed; *sum gets their total, *hit whether the run ended on an inclusive entry,
+// *bad whether a poisoned entry was met.
+__device__ __forceinline__ uint32_t look_once(const uint64_t* st, int64_t idx, int64_t lo, uint32_t epoch, uint64_t* sum,
+                                              bool* hit, bool* bad) {
   const int lane = threadIdx.x & 31;
+  const int64_t j = idx - lane;
+  uint64_t w = st_pack(kStInc, epoch, 0);
+  if (j >= lo) w = ld_relaxed_gpu_u64(st + j);
+  const uint32_t s = st_state(w, epoch);
+  const uint32_t notready = __ballot_sync(0xffffffffu, s == 0);
+  const uint32_t incs = __ballot_sync(0xffffffffu, s == kStInc);
+  const uint32_t bads = __ballot_sync(0xffffffffu, s == kStBad);
+  // the run ends at the first inclusive entry (taken) or before the first missing / poisoned one
+  const uint32_t stop_excl = notready | bads;
+  const int first_stop = stop_excl ? __ffs(stop_excl) - 1 : 32;
+  const int first_inc = incs ? __ffs(incs) - 1 : 32;
+  int take;
+  if (first_inc < first_stop) {
+    take = first_inc + 1;
+    *hit = true;
+  } else {
+    take = first_stop;
+    *hit = false;
+  }
+  *bad = bads != 0 && (__ffs(bads) - 1) == take;
+  *sum = warp_sum_u64(lane < take ? st_value(w) : 0ull);
+  return (uint32_t)take;
+}
+
+__device__ __forceinline__ uint64_t lookback(const Chain& ch, uint32_t tile, uint32_t epoch, uint64_t agg,
+                                             uint64_t limit_ns, volatile uint32_t* err_word, bool* ok) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t grp = tile >> 5, pos = tile & 31u;
   *ok = true;
   if (tile == 0) {
-    if (lane == 0) st_relaxed_gpu_u64(st, st_pack(kStInc, epoch, agg));
+    if (lane == 0) st_relaxed_gpu_u64(ch.tile_st, st_pack(kStInc, epoch, agg));
     return 0;
   }
-  if (lane == 0) st_relaxed_gpu_u64(st + tile, st_pack(kStAgg, epoch, agg));
-  uint64_t excl = 0;
-  int64_t idx = (int64_t)tile - 1;
-  bool good = true;
+  if (lane == 0) st_relaxed_gpu_u64(ch.tile_st + tile, st_pack(kStAgg, epoch, agg));
   const long long t0 = clock64();
   const long long limit_clk = (long long)limit_ns * 2;  // SM clock is at most ~2 GHz
-  while (true) {
-    const int64_t j = idx - lane;
-    uint64_t w = 0;
-    uint32_t s = kStInc;
-    uint32_t it = 0;
+  uint64_t excl = 0;
+  bool good = true, done = false;
+  uint32_t idle = 0;
+  auto stalled = [&]() -> bool {  // called after a poll that made no progress
+    ++idle;
+    if ((idle & 15u) != 15u) return false;
+    return clock64() - t0 > limit_clk || idle > (1u << 24) || *err_word >= (uint32_t)kErrTimeout;
+  };
+  // ---- level 1: the earlier tiles of this group ------------------------------------------------
+  {
+    int64_t idx = (int64_t)tile - 1;
+    const int64_t lo = (int64_t)grp * 32;
+    while (idx >= lo) {
+      uint64_t sum;
+      bool hit, bad;
+      const uint32_t n = look_once(ch.tile_st, idx, lo, epoch, &sum, &hit, &bad);
+      excl += sum;
+      idx -= n;
+      if (bad) { good = false; break; }
+      if (hit) {
+        if (idx + 1 >= lo) done = true;  // a real inclusive entry, not the virtual one below `lo`
+        break;
+      }
+      if (n == 0 && stalled()) { good = false; break; }
+    }
+  }
+  // the group's last tile knows the group aggregate now: let later groups skip over this one
+  if (good && !done && pos == 31 && lane == 0)
+    st_relaxed_gpu_u64(ch.group_st + grp, st_pack(kStAgg, epoch, excl + agg));
+  // ---- level 2: whole groups -------------------------------------------------------------------
+  if (good && !done && grp > 0) {
+    int64_t idx = (int64_t)grp - 1;
     while (true) {
-      if (j >= 0) {
-        w = ld_relaxed_gpu_u64(st + j);
-        s = st_state(w, epoch);
-      }
-      if (__all_sync(0xffffffffu, s != 0)) break;
-      ++it;
-      bool give_up = false;
-      if ((it & 15u) == 15u) {
-        __nanosleep(40);
-        give_up = (clock64() - t0 > limit_clk) || it > (1u << 24) || (*err_word >= (uint32_t)kErrTimeout);
-      }
-      if (__any_sync(0xffffffffu, give_up)) { good = false; break; }
+      uint64_t sum;
+      bool hit, bad;
+      const uint32_t n = look_once(ch.group_st, idx, 0, epoch, &sum, &hit, &bad);
+      excl += sum;
+      idx -= n;
+      if (bad) { good = false; break; }
+      if (hit) break;  // a group's inclusive prefix, or the virtual zero before group 0
+      if (n == 0 && stalled()) { good = false; break; }
     }
-    if (!good) break;
-    if (__any_sync(0xffffffffu, s == kStBad)) { good = false; break; }
-    uint64_t v = (j >= 0) ? st_value(w) : 0ull;
-    const uint32_t incmask = __ballot_sync(0xffffffffu, s == kStInc);
-    if (incmask) {
-      const int first = __ffs(incmask) - 1;
-      excl += warp_sum_u64(lane <= first ? v : 0ull);
-      break;
-    }
-    excl += warp_sum_u64(v);
-    idx -= 32;
   }
   if (lane == 0) {
-    st_relaxed_gpu_u64(st + tile, st_pack(good ? kStInc : kStBad, epoch, excl + agg));
+    const uint64_t word = st_pack(good ? kStInc : kStBad, epoch, excl + agg);
+    st_relaxed_gpu_u64(ch.tile_st + tile, word);
+    if (pos == 31) st_relaxed_gpu_u64(ch.group_st + grp, word);
     if (!good) atomicMax((uint32_t*)err_word, (uint32_t)kErrTimeout);
   }
   *ok = good;
@@ -385,17 +451,17 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, u
 }
 
 // Moves the `tot` payload bytes packed at obuf[0..tot) to global byte offset `goff` of every
-// destination, with aligned 16-byte stores wherever a whole unit belongs to this tile (run by one
-// warp).  16 readable guard bytes must precede and follow obuf.  All destinations share the same
-// 16-byte phase.
-__device__ __forceinline__ void copy_out_warp(const uint8_t* obuf, uint8_t* const* outs, uint32_t n_dst, uint64_t goff,
-                                              uint32_t tot, int lane) {
+// destination, with aligned 16-byte stores wherever a whole unit belongs to this tile (run by
+// `nthr` threads, this one being number `t`).  16 readable guard bytes must precede and follow
+// obuf.  All destinations share the same 16-byte phase.
+__device__ __forceinline__ void copy_out(const uint8_t* obuf, uint8_t* const* outs, uint32_t n_dst, uint64_t goff,
+                                         uint32_t tot, uint32_t t, uint32_t nthr) {
   if (tot == 0) return;
   const uint32_t phase = (uint32_t)((reinterpret_cast<uintptr_t>(outs[0]) + goff) & 15u);
   const uint32_t nvec = (phase + tot + 15u) >> 4;
   const uint32_t sh = ((16u - phase) & 3u) * 8u;
   const uint32_t lo_valid = phase, hi_valid = phase + tot;
-  for (uint32_t v = lane; v < nvec; v += 32) {
+  for (uint32_t v = t; v < nvec; v += nthr) {
     const int so = (int)(16u * v) - (int)phase;
     const uint32_t* wp = reinterpret_cast<const uint32_t*>(obuf + (so & ~3));
     uint32_t w0 = wp[0], w1 = wp[1], w2 = wp[2], w3 = wp[3], w4 = sh ? wp[4] : 0u;
