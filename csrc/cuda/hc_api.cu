@@ -148,10 +148,11 @@ int hc_decompress(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, fl
   if (n == 0) return hc::kOk;
   hc::DecParams p;
   memset(&p, 0, sizeof(p));
-  p.in = d_in;
-  p.in_size = in_size;
-  p.out = d_x;
-  p.n = n;
+  p.n_seg = 1;
+  p.seg[0].in = d_in;
+  p.seg[0].in_size = in_size;
+  p.seg[0].out = d_x;
+  p.seg[0].n = n;
   p.eb = eb;
   p.ws = next_workspace(c, stream);
   return hc::launch_decode(mode, p, stream) == cudaSuccess ? hc::kOk : hc::kErrCuda;

@@ -376,7 +376,7 @@ struct __align__(16) DecShared {
 
 template <int MODE>
 __global__ void __launch_bounds__(kDecThreads, 3)
-hc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecParams p) {
+hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ DecShared sh;
@@ -387,10 +387,8 @@ hc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecParams p) {
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const Workspace& ws = p.ws;
-  const bool tma = p.use_tma != 0;
   const float eb = p.eb;
-  const uint64_t nrate = rate_bytes(p.n);
-  const uint64_t full_rows = p.n / kBlock;
+  const uint32_t groups_per_seg = p.tiles_per_seg / 32 + 1;
 
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -405,12 +403,13 @@ hc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecParams p) {
 
   if (warp == kComputeThreads / 32) {
     // ================================ loader warp ================================================
+    uint32_t next_tile = kNoTile;
+    if (lane == 0 && !*abort) next_tile = atomicAdd(ws.ctrl, 1u);
     for (uint32_t k = 0;; ++k) {
       const int s = k & 1;
-      uint32_t tile = kNoTile;
-      if (lane == 0 && !*abort) tile = atomicAdd(ws.ctrl, 1u);
-      tile = __shfl_sync(0xffffffffu, tile, 0);
+      uint32_t tile = __shfl_sync(0xffffffffu, next_tile, 0);
       if (tile >= p.n_tiles) tile = kNoTile;
+      if (tile != kNoTile && lane == 0) next_tile = *abort ? kNoTile : atomicAdd(ws.ctrl, 1u);
       if (k >= 2 && !wait_or_flag(&sh.in_free[s], ((k >> 1) - 1) & 1, ws, abort)) tile = kNoTile;
       if (lane == 0) sh.tile[k & 3] = tile;
       if (tile == kNoTile) {
@@ -418,17 +417,20 @@ hc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecParams p) {
         if (lane == 0) mbar_arrive(&sh.in_full[s]);
         break;
       }
+      const uint32_t sg = tile / p.tiles_per_seg, lt = tile - sg * p.tiles_per_seg;
+      const DecSegment& seg = p.seg[sg];
       bool usable = true;
-      if (p.in_ready) {
+      if (seg.in_ready) {
         uint32_t okf = 1;
-        if (lane == 0) okf = wait_flag(p.in_ready + tile, p.ring_epoch, ws.spin_limit_ns, ws.ctrl + 2) ? 1u : 0u;
+        if (lane == 0) okf = wait_flag(seg.in_ready + lt, p.ring_epoch, ws.spin_limit_ns, ws.ctrl + 2) ? 1u : 0u;
         okf = __shfl_sync(0xffffffffu, okf, 0);
         if (!okf) {
           if (lane == 0) note_error(ws.ctrl, kErrPeer);
           usable = false;
         }
       }
-      loader_stage_stream(p.in, p.in_size, nrate, tile, Chain{ws.st_a, ws.grp_a}, ws, cbuf[s], &sh.in_full[s], sh.in_rel[s],
+      const Chain chain{ws.st_a + (size_t)sg * p.tiles_per_seg, ws.grp_a + (size_t)sg * groups_per_seg};
+      loader_stage_stream(seg.in, seg.in_size, rate_bytes(seg.n), lt, chain, ws, cbuf[s], &sh.in_full[s], sh.in_rel[s],
                           sh.in_rate[s], &sh.in_phase[s], usable);
       if (lane == 0 && fatal_error(ws.ctrl)) *abort = 1;
     }
@@ -439,6 +441,10 @@ hc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecParams p) {
       bool alive = wait_or_flag(&sh.in_full[s], (k >> 1) & 1, ws, abort);
       const uint32_t tile = alive ? sh.tile[k & 3] : kNoTile;
       if (tile == kNoTile) break;
+      const uint32_t sg = tile / p.tiles_per_seg, lt = tile - sg * p.tiles_per_seg;
+      const DecSegment& seg = p.seg[sg];
+      const bool tma = seg.use_tma != 0;
+      const uint64_t full_rows = seg.n / kBlock;
       const uint32_t rate = sh.in_rate[s][tid];
       const uint32_t pos = sh.in_phase[s] + sh.in_rel[s][tid];
       int W = plane_width(rate & 31u);
@@ -456,28 +462,30 @@ hc_decode_kernel(const __grid_constant__ CUtensorMap tmap, const DecParams p) {
 #pragma unroll
       for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(__fmul_rn(__fmul_rn((float)d[i], eb), 2.0f));
 
-      const uint64_t row = (uint64_t)tile * kTileBlocks + tid;
-      const bool ragged = row * kBlock < p.n && (row + 1) * kBlock > p.n;
+      const uint64_t row = (uint64_t)lt * kTileBlocks + tid;
+      const bool ragged = row * kBlock < seg.n && (row + 1) * kBlock > seg.n;
+      // the TMA store that used obuf[s] two tiles ago must have finished reading it (every turn
+      // commits exactly one group, empty when the tile goes out with plain stores)
+      if (tid == 0) tma_wait_group_read<1>();
+      compute_barrier();
       if (tma) {
-        // the TMA store that used obuf[s] two tiles ago must have finished reading it
-        if (tid == 0) tma_wait_group_read<1>();
-        compute_barrier();
         store_row_swizzled(obuf[s], tid, w);
         fence_proxy_async();
-        compute_barrier();
-        if (tid == 0) {
-          if ((uint64_t)tile * kTileBlocks < full_rows) tma_store_2d(&tmap, 0, (int)(tile * kTileBlocks), obuf[s]);
-          tma_commit_group();  // an empty group keeps the two-deep accounting uniform
-        }
+      }
+      compute_barrier();
+      if (tid == 0) {
+        if (tma && (uint64_t)lt * kTileBlocks < full_rows)
+          tma_store_2d(&tmaps.m[sg], 0, (int)(lt * kTileBlocks), obuf[s]);
+        tma_commit_group();
       }
       if (!tma || ragged) {
         const uint64_t o = row * kBlock;
 #pragma unroll
         for (int i = 0; i < 32; ++i)
-          if (o + i < p.n) p.out[o + i] = __uint_as_float(w[i]);
+          if (o + i < seg.n) seg.out[o + i] = __uint_as_float(w[i]);
       }
     }
-    if (tid == 0 && tma) tma_wait_group<0>();
+    if (tid == 0) tma_wait_group<0>();
   }
   cta_epilogue(ws.ctrl);
 }
@@ -618,7 +626,7 @@ cudaError_t launch_encode_m(int mode, const CUtensorMap& map, const EncParams& p
 }
 
 template <int MODE>
-cudaError_t launch_decode_t(const CUtensorMap& map, const DecParams& p, int grid, cudaStream_t stream) {
+cudaError_t launch_decode_t(const TensorMaps& maps, const DecParams& p, int grid, cudaStream_t stream) {
   static thread_local bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -627,24 +635,28 @@ cudaError_t launch_decode_t(const CUtensorMap& map, const DecParams& p, int grid
     if (e != cudaSuccess) return e;
     attr_done[dev & 63] = true;
   }
-  dev::hc_decode_kernel<MODE><<<grid, dev::kDecThreads, kDecSmem, stream>>>(map, p);
+  dev::hc_decode_kernel<MODE><<<grid, dev::kDecThreads, kDecSmem, stream>>>(maps, p);
   return cudaGetLastError();
 }
 
 }  // namespace
 
+// sized for max_elems values split over up to kMaxDst segments (each rounded up to whole chunks)
+static size_t workspace_tiles(size_t max_elems) {
+  return rate_bytes(max_elems) / kTileBlocks + (size_t)kMaxDst * (kBlocksPerChunk / kTileBlocks) + 1;
+}
 size_t workspace_bytes(size_t max_elems) {
-  size_t tiles = rate_bytes(max_elems) / kTileBlocks + 1;
-  size_t groups = tiles / 32 + 1;
+  size_t tiles = workspace_tiles(max_elems);
+  size_t groups = tiles / 32 + 1 + kMaxDst;
   return 256 + 3 * (tiles + groups) * sizeof(uint64_t);
 }
 
 Workspace workspace_view(void* mem, size_t max_elems, uint32_t epoch, uint64_t spin_limit_ns) {
-  size_t tiles = rate_bytes(max_elems) / kTileBlocks + 1;
+  size_t tiles = workspace_tiles(max_elems);
   Workspace w;
   uint8_t* b = static_cast<uint8_t*>(mem);
   w.ctrl = reinterpret_cast<uint32_t*>(b);
-  size_t groups = tiles / 32 + 1;
+  size_t groups = tiles / 32 + 1 + kMaxDst;
   w.st_a = reinterpret_cast<uint64_t*>(b + 256);
   w.st_b = w.st_a + tiles;
   w.st_out = w.st_b + tiles;
@@ -684,16 +696,21 @@ cudaError_t launch_encode(int op, int mode, EncParams p, cudaStream_t stream) {
 }
 
 cudaError_t launch_decode(int mode, DecParams p, cudaStream_t stream) {
-  if (p.n == 0) return cudaSuccess;
-  p.n_tiles = (uint32_t)(rate_bytes(p.n) / kTileBlocks);
-  CUtensorMap map;
-  memset(&map, 0, sizeof(map));
-  p.use_tma = make_rows_map(&map, p.out, p.n / kBlock) ? 1u : 0u;
+  if (p.n_seg == 0 || p.n_seg > (uint32_t)kMaxDst) return cudaErrorInvalidValue;
+  uint64_t n_max = 0;
+  for (uint32_t i = 0; i < p.n_seg; ++i) n_max = p.seg[i].n > n_max ? p.seg[i].n : n_max;
+  if (n_max == 0) return cudaSuccess;
+  p.tiles_per_seg = (uint32_t)(rate_bytes(n_max) / kTileBlocks);
+  p.n_tiles = p.tiles_per_seg * p.n_seg;
+  TensorMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  for (uint32_t i = 0; i < p.n_seg; ++i)
+    p.seg[i].use_tma = make_rows_map(&maps.m[i], p.seg[i].out, p.seg[i].n / kBlock) ? 1u : 0u;
   int grid = grid_for_tiles(p.n_tiles, 3);
   switch (mode) {
     case kModeOutlier:
-    case kModePlain: return launch_decode_t<kModeOutlier>(map, p, grid, stream);
-    case kModeVec: return launch_decode_t<kModeVec>(map, p, grid, stream);
+    case kModePlain: return launch_decode_t<kModeOutlier>(maps, p, grid, stream);
+    case kModeVec: return launch_decode_t<kModeVec>(maps, p, grid, stream);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -76,17 +76,29 @@ struct EncParams {
   Workspace ws;
 };
 
-struct DecParams {
+// One decode launch can take several independent streams ("segments"): the all-gather phase of a
+// collective decodes the P reduced chunks with one kernel.  Every segment owns tiles_per_seg
+// consecutive tile tickets and its own look-back chain.
+struct DecSegment {
   const uint8_t* in;
   uint64_t in_size;
-  const uint32_t* in_ready;
-  uint32_t ring_epoch;
+  const uint32_t* in_ready;  // one arrival flag per tile, or null
   float* out;
   uint64_t n;
-  uint32_t n_tiles;
   uint32_t use_tma;
+  uint32_t pad;
+};
+struct DecParams {
+  DecSegment seg[kMaxDst];
+  uint32_t n_seg;
+  uint32_t tiles_per_seg;
+  uint32_t n_tiles;  // n_seg * tiles_per_seg
+  uint32_t ring_epoch;
   float eb;
   Workspace ws;
+};
+struct TensorMaps {
+  CUtensorMap m[kMaxDst];
 };
 
 namespace dev {

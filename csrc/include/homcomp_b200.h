@@ -84,6 +84,33 @@ int hc_sum(float* d_dst, const float* d_a, const float* d_b, const float* d_c, c
            hc_stream_t stream);
 const char* hc_status_string(int status);
 
+// ---- compressed collectives over peer-mapped memory ------------------------------------------
+// One process (or thread) per GPU.  Every rank provides a zeroed "symmetric" device region of
+// hc_comm_symmetric_bytes() bytes that all other ranks can address (CUDA IPC mapping, a symmetric
+// heap, peer access inside one process); peer_bases[r] is rank r's region as seen from this rank.
+// All data movement is done by the kernels themselves with peer stores; there is no MPI or NCCL
+// call on this path.  Counterpart of allreduce_ring_comprs_hom_sum_F
+// (HomComp/src/cuda_awareallreduce.cu:166-264).
+typedef struct hc_comm hc_comm;
+size_t hc_comm_symmetric_bytes(int world, size_t max_count);
+// mc_base: multicast (NVLS) mapping of the same region, or NULL to use peer stores only
+int hc_comm_create(hc_comm** out, int rank, int world, size_t max_count, void* const* peer_bases, void* mc_base);
+void hc_comm_destroy(hc_comm* c);
+int hc_comm_set_timeout_ms(hc_comm* c, unsigned ms);
+int hc_comm_status(hc_comm* c, int clear);  // synchronises; sticky hc::Status
+// Sum of `count` floats over all ranks, error at most world * eb per value; d_sbuf and d_rbuf may
+// alias.  Enqueues world + 1 kernels on `stream`; never allocates or synchronises.
+int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, float eb, hc_stream_t stream);
+// device-side counters of the last call: bytes[s] = stream bytes this rank produced at step s
+int hc_comm_last_stream_bytes(hc_comm* c, uint64_t* bytes, int n);
+
+// CUDA IPC helpers for the multi-process bootstrap (the 64-byte handle travels over any host
+// channel: torch.distributed, MPI, a file)
+int hc_ipc_alloc(void** d_ptr, size_t bytes, uint8_t handle[64]);
+int hc_ipc_open(const uint8_t handle[64], void** d_ptr);
+int hc_ipc_close(void* d_ptr);
+int hc_ipc_free(void* d_ptr);
+
 #ifdef __cplusplus
 }
 #endif

@@ -8,7 +8,21 @@ vp = C.c_void_p
 
 def declare(lib):
     sz, f, i, u = C.c_size_t, C.c_float, C.c_int, C.c_uint
-    sigs = {}
+    lib.hc_comm_symmetric_bytes.restype = sz
+    lib.hc_comm_symmetric_bytes.argtypes = [i, sz]
+    lib.hc_comm_destroy.restype = None
+    lib.hc_comm_destroy.argtypes = [vp]
+    sigs = {
+        "hc_comm_create": [C.POINTER(vp), i, i, sz, C.POINTER(vp), vp],
+        "hc_comm_set_timeout_ms": [vp, u],
+        "hc_comm_status": [vp, i],
+        "hc_allreduce": [vp, vp, vp, sz, f, vp],
+        "hc_comm_last_stream_bytes": [vp, C.POINTER(C.c_uint64), i],
+        "hc_ipc_alloc": [C.POINTER(vp), sz, C.c_char_p],
+        "hc_ipc_open": [C.c_char_p, C.POINTER(vp)],
+        "hc_ipc_close": [vp],
+        "hc_ipc_free": [vp],
+    }
     for name, args in sigs.items():
         if hasattr(lib, name):
             fn = getattr(lib, name)

@@ -1,0 +1,1 @@
+from .comm import CompressedAllreduce  # noqa: F401

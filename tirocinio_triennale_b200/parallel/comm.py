@@ -1,0 +1,109 @@
+"""Compressed allreduce over NVLink peer memory, one process per GPU.
+
+``torch.distributed`` is used for the bootstrap only (exchange of CUDA IPC handles, barriers); the
+data path is the library's own kernels storing into peer memory.  The reference passes every
+compressed chunk through MPI point-to-point calls (HomComp/src/cuda_awareallreduce.cu:208-255).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from .. import _lib
+
+
+class CompressedAllreduce:
+    """Handle-based compressed ring allreduce for float32 CUDA tensors of up to ``max_count`` values.
+
+    Every call enqueues ``world + 1`` kernels on the current stream: it never allocates, never
+    synchronises the host and never copies a size to the host.  The result is identical on all
+    ranks and equals ``2 * eb * sum_r quantise(x_r)``: the error is at most ``world * eb``.
+    """
+
+    def __init__(self, max_count: int, group=None, device=None, timeout_ms: int | None = None):
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed must be initialised (it carries the IPC handles)")
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.max_count = int(max_count)
+        self.lib = _lib.cuda()
+        self._peers = {}
+        self._base = None
+        self._h = None
+        with torch.cuda.device(self.device):
+            nbytes = int(self.lib.hc_comm_symmetric_bytes(self.world, self.max_count))
+            base = C.c_void_p()
+            handle = C.create_string_buffer(64)
+            _lib.check(self.lib.hc_ipc_alloc(C.byref(base), nbytes, handle), "ipc_alloc")
+            self._base = base
+            self.symmetric_bytes = nbytes
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            ptrs = (C.c_void_p * self.world)()
+            for r in range(self.world):
+                if r == self.rank:
+                    ptrs[r] = base.value
+                else:
+                    p = C.c_void_p()
+                    _lib.check(self.lib.hc_ipc_open(handles[r], C.byref(p)), "ipc_open(rank %d)" % r)
+                    self._peers[r] = p
+                    ptrs[r] = p.value
+            h = C.c_void_p()
+            _lib.check(self.lib.hc_comm_create(C.byref(h), self.rank, self.world, self.max_count, ptrs, None),
+                       "comm_create")
+            self._h = h
+            if timeout_ms:
+                _lib.check(self.lib.hc_comm_set_timeout_ms(self._h, int(timeout_ms)), "set_timeout")
+            torch.cuda.synchronize()
+        dist.barrier(group=group)  # every region is zeroed and mapped before the first store
+
+    def allreduce(self, send: torch.Tensor, recv: torch.Tensor | None = None, eb: float = 1e-4) -> torch.Tensor:
+        if send.dtype != torch.float32 or not send.is_cuda or not send.is_contiguous():
+            raise ValueError("expected a contiguous float32 CUDA tensor")
+        if recv is None:
+            recv = send
+        n = send.numel()
+        if n > self.max_count or recv.numel() != n:
+            raise ValueError("tensor larger than the handle's max_count")
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.hc_allreduce(self._h, send.data_ptr(), recv.data_ptr(), n, eb,
+                                             torch.cuda.current_stream().cuda_stream), "allreduce")
+        return recv
+
+    def status(self, clear: bool = True) -> int:
+        with torch.cuda.device(self.device):
+            return int(self.lib.hc_comm_status(self._h, 1 if clear else 0))
+
+    def last_stream_bytes(self):
+        """Stream bytes this rank produced at each step of the last call (synchronises)."""
+        arr = (C.c_uint64 * 16)()
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.hc_comm_last_stream_bytes(self._h, arr, 16), "last_stream_bytes")
+        return list(arr)[: self.world]
+
+    def close(self):
+        if self._h is None:
+            return
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            try:
+                dist.barrier(group=self.group)  # nobody may still be storing into a region about to go away
+            except Exception:
+                pass
+            self.lib.hc_comm_destroy(self._h)
+            self._h = None
+            for p in self._peers.values():
+                self.lib.hc_ipc_close(p)
+            self._peers = {}
+            self.lib.hc_ipc_free(self._base)
+            self._base = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
