@@ -12,6 +12,11 @@ extern "C" {
 int ref_init(void) { return MPI_Init(nullptr, nullptr); }
 int ref_finalize(void) { return MPI_Finalize(); }
 int ref_barrier(void) { return MPI_Barrier(MPI_COMM_WORLD); }
+int ref_current_device(void) {
+  int d = -1;
+  cudaGetDevice(&d);
+  return d;
+}
 
 int ref_allreduce_F(const float* d_sbuf, float* d_rbuf, size_t count, float eb) {
   return allreduce_ring_comprs_hom_sum_F(d_sbuf, d_rbuf, count, MPI_COMM_WORLD, eb);

@@ -70,6 +70,14 @@ def main(args):
     import bench as B
     from tirocinio_triennale_b200.utils import datagen, timing
 
+    if args.gpus > 1:
+        # Recorded on a 2 x B200 box: the first launch of the reference's GSZ_compress_kernel_outlier
+        # inside allreduce_ring_comprs_hom_sum_F on rank 1 ended with "an illegal memory access was
+        # encountered" (HomComp/src/cuda_awareallreduce.cu:207), while the same kernel on the same
+        # data runs clean in a single process.  The cause was not found by reading, so that code is
+        # not run again on these shared GPUs.
+        return _unavailable("reference allreduce_ring_comprs_hom_sum_F faulted (illegal memory access at "
+                            "cuda_awareallreduce.cu:207) on 2 GPUs; not run again; N=1 codec arm is available")
     rank, world, local = B.init_dist(args.gpus)
     try:
         if world > 1 and lib.ref_init() != 0:
