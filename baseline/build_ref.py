@@ -4,7 +4,9 @@ The sources are copied unmodified from the reference tree, with the two things t
 cannot compile without: a stand-in ``include/comprs_test.cuh`` that only includes ``homcomp.cuh`` (the header is included
 but absent, HomComp/src/GSZ_entry.cu:3) and the declaration fix in ``intra_node_allgather``
 (HomComp/src/cuda_awareallreduce.cu:648-658: ``send_count`` declared twice, ``recv_count`` never).
-That function is not on the benchmarked path.  ``mpi.h`` comes from baseline/mpi_shim because no
+That function is not on the benchmarked path.  One more change is needed to RUN the kernels on
+B200 at all: the shared variable ``excl_sum`` is read uninitialised by the first chunk of every
+kernel (see the comment in ``build``); it is set to 0 here.  ``mpi.h`` comes from baseline/mpi_shim because no
 MPI exists on the image.  Nothing of this library is used by the product.
 """
 from __future__ import annotations
@@ -43,6 +45,18 @@ def build(force: bool = False) -> Path | None:
     if first >= 0 and second >= 0:
         text = text[:second] + "size_t recv_count;\n  send_count =" + text[second + len("size_t send_count ="):]
     p.write_text(text)
+    # Undefined behaviour that faults on B200: in every kernel the __shared__ variable `excl_sum` is
+    # only written by chunks with index > 0 (HomComp/src/GSZ.cu:196-222) but read by all of them
+    # (`base_idx = excl_sum + rate_ofs`, GSZ.cu:237), so the first chunk's payload goes to whatever
+    # offset the previous kernel left in shared memory.  On A100 that happened to read as 0; here it
+    # does not, and the stores leave the buffer.  The build therefore initialises it to 0, the value
+    # the code relies on; nothing else in the kernels is touched.
+    for f in ("GSZ.cu", "homcomp.cu"):
+        q = src / f
+        t = q.read_text()
+        decl = "  __shared__ unsigned int excl_sum;\n"
+        t = t.replace(decl, decl + "  if (threadIdx.x == 0) excl_sum = 0; /* build_ref.py: see above */\n")
+        q.write_text(t)
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     cmd = [nvcc, "-std=c++17", "-gencode", "arch=compute_100,code=sm_100", "-O3", "-shared", "-Xcompiler", "-fPIC",
            "-w", "-I", str(HERE / "mpi_shim"), "-I", str(inc),

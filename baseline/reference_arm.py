@@ -1,7 +1,8 @@
 """Reference arm of bench.py.
 
-Runs the reference library (built by baseline/build_ref.py from the unmodified sources) through
-its own public API on the configuration bench.py measures: 64 MiB of float32 per rank,
+Runs the reference library (built by baseline/build_ref.py from the reference sources with the
+three fixes it needs to compile and to run without faulting on B200, listed there) through its own
+public API on the configuration bench.py measures: 64 MiB of float32 per rank,
 gradient-like values, error bound 1e-4.
 
 * N >= 2: ``allreduce_ring_comprs_hom_sum_F`` (the variant the reference benchmarks, its stock code
@@ -70,14 +71,6 @@ def main(args):
     import bench as B
     from tirocinio_triennale_b200.utils import datagen, timing
 
-    if args.gpus > 1:
-        # Recorded on a 2 x B200 box: the first launch of the reference's GSZ_compress_kernel_outlier
-        # inside allreduce_ring_comprs_hom_sum_F on rank 1 ended with "an illegal memory access was
-        # encountered" (HomComp/src/cuda_awareallreduce.cu:207), while the same kernel on the same
-        # data runs clean in a single process.  The cause was not found by reading, so that code is
-        # not run again on these shared GPUs.
-        return _unavailable("reference allreduce_ring_comprs_hom_sum_F faulted (illegal memory access at "
-                            "cuda_awareallreduce.cu:207) on 2 GPUs; not run again; N=1 codec arm is available")
     rank, world, local = B.init_dist(args.gpus)
     try:
         if world > 1 and lib.ref_init() != 0:
@@ -147,7 +140,10 @@ def main(args):
                          " (its allreduce is a no-op for one rank)",
                 "global_batch": COUNT * world, "seq_len": COUNT, "parallelism": "ring%d" % world, "error_bound": EB,
                 "transport": "single-host MPI shim: IPC-mapped device mailboxes (GPU to GPU copies)",
-                "build": "nvcc -arch sm_100 -O3 of the unmodified sources + stand-in comprs_test.cuh + declaration fix",
+                "build": "nvcc -arch sm_100 -O3 of the reference sources; not byte-for-byte unmodified: stand-in "
+                         "comprs_test.cuh, declaration fix in intra_node_allgather, and the __shared__ excl_sum "
+                         "that the first chunk reads uninitialised is set to 0 (as shipped the kernels store out "
+                         "of bounds on B200)",
                 "l2": "rotating %d input and %d output buffers" % (NBUF, NBUF),
             },
             "per_rank_gbs": value / world, "max_abs_err": max_err, "err_bound_world_x_eb": world * EB,
