@@ -35,6 +35,7 @@ struct Layout {
   size_t flag_bytes = 0;  // flags of one slot
   size_t n_slots = 0;
   size_t flags_off = 0;
+  size_t raw_flags_off = 0;
   size_t total = 0;
   Layout(int P, size_t max_count) {
     world = P;
@@ -43,8 +44,13 @@ struct Layout {
     flag_bytes = round_up((hc::rate_bytes(chunk_max) / hc::kTileBlocks + 1) * sizeof(uint32_t), kAlign);
     n_slots = (size_t)(P - 1) + 2 * (size_t)P;
     flags_off = n_slots * slot_bytes;
-    total = flags_off + n_slots * flag_bytes;
+    raw_flags_off = flags_off + n_slots * flag_bytes;
+    total = raw_flags_off + 4096;
   }
+  // uncompressed two-shot allreduce: staging area S (count floats) at the start of the region,
+  // result area R right behind it; three flag rows of `world` uint32 each
+  size_t raw_capacity_floats() const { return flags_off / (2 * sizeof(float)); }
+  size_t raw_flag(int row, int rank) const { return raw_flags_off + ((size_t)row * 64 + rank) * sizeof(uint32_t); }
   size_t rs_slot(int s) const { return (size_t)(s - 1); }                       // s in 1..P-1
   size_t ag_slot(int parity, int c) const { return (size_t)(world - 1) + (size_t)parity * world + c; }
   size_t data_off(size_t slot) const { return slot * slot_bytes; }
@@ -64,6 +70,7 @@ struct hc_comm {
   uint64_t* sizes = nullptr;   // device words: stream size produced at each step of the last call
   uint32_t ws_epoch = 0;
   uint32_t call = 0;
+  uint32_t raw_call = 0;
   uint64_t spin_limit_ns = 2000ull * 1000 * 1000;
 };
 
@@ -223,6 +230,151 @@ int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, f
   d.ws = next_ws(c, stream);
   if (hc::launch_decode(hc::kModeOutlier, d, stream) != cudaSuccess) return hc::kErrCuda;
   return hc::kOk;
+}
+
+// ---- uncompressed allreduce over the same peer mappings ------------------------------------------
+// Two-shot direct algorithm for NVSwitch: every rank stages its input in its symmetric region,
+// rank r sums chunk r over all ranks (peer loads, fixed rank order, so the result is bit-identical
+// everywhere) and stores it into every rank's result area (peer stores).  Takes the place of the
+// reference's Open-MPI-style uncompressed ring (allreduce_ring_gpu,
+// HomComp/src/cuda_awareallreduce.cu:895-1038) and of the raw intra-node phases of its hierarchical
+// allreduce (:588-671).
+namespace {
+
+struct RawParams {
+  const float* src;
+  float* dst;
+  uint64_t count;
+  uint64_t chunk;  // floats per rank
+  int rank, world;
+  uint32_t call;
+  uint8_t* peer[hc::kMaxDst];
+  uint64_t s_off, r_off;          // byte offsets of the staging / result areas in a region
+  uint64_t flag_off[3];           // staged, reduced, done rows
+  uint32_t* ctrl;                 // [1] CTA exit counter, [2] status
+  uint64_t limit_ns;
+};
+
+__device__ __forceinline__ bool raw_wait(const uint32_t* f, uint32_t want, const RawParams& p) {
+  return hc::dev::wait_flag(f, want, p.limit_ns, p.ctrl + 2);
+}
+
+// the last CTA to finish raises this rank's flag of `row` on every peer
+__device__ __forceinline__ void raw_publish(const RawParams& p, int row) {
+  __syncthreads();
+  __shared__ uint32_t last;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    last = atomicAdd(p.ctrl + 1, 1u) == gridDim.x - 1 ? 1u : 0u;
+  }
+  __syncthreads();
+  if (last) {
+    if ((int)threadIdx.x < p.world) {
+      __threadfence_system();
+      hc::dev::st_release_sys_u32(reinterpret_cast<uint32_t*>(p.peer[threadIdx.x] + p.flag_off[row]) + p.rank, p.call);
+    }
+    if (threadIdx.x == 0) p.ctrl[1] = 0;
+  }
+}
+
+__global__ void __launch_bounds__(256) hc_raw_stage_kernel(const RawParams p) {
+  float* S = reinterpret_cast<float*>(p.peer[p.rank] + p.s_off);
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, i0 = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool al = ((reinterpret_cast<uintptr_t>(p.src) & 15u) == 0);
+  const uint64_t n4 = al ? p.count / 4 : 0;
+  for (uint64_t i = i0; i < n4; i += stride) reinterpret_cast<float4*>(S)[i] = reinterpret_cast<const float4*>(p.src)[i];
+  for (uint64_t i = n4 * 4 + i0; i < p.count; i += stride) S[i] = p.src[i];
+  raw_publish(p, 0);
+}
+
+__global__ void __launch_bounds__(256) hc_raw_reduce_kernel(const RawParams p) {
+  const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.flag_off[0]);
+  const uint32_t* done = reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.flag_off[2]);
+  __shared__ uint32_t ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < p.world) {
+    // everybody has staged this call's input and has finished reading the previous call's result
+    bool good = raw_wait(mine + threadIdx.x, p.call, p);
+    if (good && p.call > 1) good = raw_wait(done + threadIdx.x, p.call - 1, p);
+    if (!good) {
+      atomicMax(p.ctrl + 2, (uint32_t)hc::kErrPeer);
+      ok = 0;
+    }
+  }
+  __syncthreads();
+  const uint64_t lo = (uint64_t)p.rank * p.chunk;
+  const uint64_t hi = lo + p.chunk < p.count ? lo + p.chunk : p.count;
+  if (ok && lo < hi) {
+    const uint64_t n = hi - lo, n4 = n / 4;  // chunk starts are multiples of 32 floats
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, i0 = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (uint64_t i = i0; i < n4; i += stride) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int q = 0; q < p.world; ++q) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(p.peer[q] + p.s_off) + lo / 4 + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      for (int q = 0; q < p.world; ++q) reinterpret_cast<float4*>(p.peer[q] + p.r_off)[lo / 4 + i] = acc;
+    }
+    for (uint64_t i = n4 * 4 + i0; i < n; i += stride) {
+      float acc = 0.f;
+      for (int q = 0; q < p.world; ++q) acc += __ldcg(reinterpret_cast<const float*>(p.peer[q] + p.s_off) + lo + i);
+      for (int q = 0; q < p.world; ++q) reinterpret_cast<float*>(p.peer[q] + p.r_off)[lo + i] = acc;
+    }
+  }
+  raw_publish(p, 1);
+}
+
+__global__ void __launch_bounds__(256) hc_raw_gather_kernel(const RawParams p) {
+  const uint32_t* red = reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.flag_off[1]);
+  __shared__ uint32_t ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < p.world && !raw_wait(red + threadIdx.x, p.call, p)) {
+    atomicMax(p.ctrl + 2, (uint32_t)hc::kErrPeer);
+    ok = 0;
+  }
+  __syncthreads();
+  if (ok) {
+    const float* R = reinterpret_cast<const float*>(p.peer[p.rank] + p.r_off);
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, i0 = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool al = ((reinterpret_cast<uintptr_t>(p.dst) & 15u) == 0);
+    const uint64_t n4 = al ? p.count / 4 : 0;
+    for (uint64_t i = i0; i < n4; i += stride) reinterpret_cast<float4*>(p.dst)[i] = __ldcg(reinterpret_cast<const float4*>(R) + i);
+    for (uint64_t i = n4 * 4 + i0; i < p.count; i += stride) p.dst[i] = __ldcg(R + i);
+  }
+  raw_publish(p, 2);
+}
+
+}  // namespace
+
+extern "C" int hc_allreduce_raw(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, hc_stream_t stream) {
+  if (!c || !d_sbuf || !d_rbuf) return hc::kErrArgument;
+  if (count == 0) return hc::kOk;
+  const Layout& L = c->lay;
+  if (count > L.raw_capacity_floats()) return hc::kErrArgument;
+  c->raw_call += 1;
+  if (c->raw_call == 0) c->raw_call = 1;
+  RawParams p;
+  memset(&p, 0, sizeof(p));
+  p.src = d_sbuf;
+  p.dst = d_rbuf;
+  p.count = count;
+  p.chunk = hc_chunk_elems(count, c->world);
+  p.rank = c->rank;
+  p.world = c->world;
+  p.call = c->raw_call;
+  for (int r = 0; r < c->world; ++r) p.peer[r] = c->peer[r];
+  p.s_off = 0;
+  p.r_off = (uint64_t)L.raw_capacity_floats() * sizeof(float);
+  for (int k = 0; k < 3; ++k) p.flag_off[k] = L.raw_flag(k, 0);
+  p.ctrl = static_cast<uint32_t*>(c->ws_mem) + 32;  // own counters, apart from the codec's
+  p.limit_ns = c->spin_limit_ns;
+  const int grid = 148 * 4;
+  hc_raw_stage_kernel<<<grid, 256, 0, stream>>>(p);
+  hc_raw_reduce_kernel<<<grid, 256, 0, stream>>>(p);
+  hc_raw_gather_kernel<<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? hc::kOk : hc::kErrCuda;
 }
 
 // ---- CUDA IPC helpers ---------------------------------------------------------------------------

@@ -101,6 +101,9 @@ int hc_comm_status(hc_comm* c, int clear);  // synchronises; sticky hc::Status
 // Sum of `count` floats over all ranks, error at most world * eb per value; d_sbuf and d_rbuf may
 // alias.  Enqueues world + 1 kernels on `stream`; never allocates or synchronises.
 int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, float eb, hc_stream_t stream);
+// Uncompressed sum over the same peer mappings (two-shot direct algorithm, three kernels); the
+// compressed and the uncompressed collective of one handle must not be in flight together.
+int hc_allreduce_raw(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, hc_stream_t stream);
 // device-side counters of the last call: bytes[s] = stream bytes this rank produced at step s
 int hc_comm_last_stream_bytes(hc_comm* c, uint64_t* bytes, int n);
 

@@ -44,3 +44,40 @@ def test_allreduce_matches_host_oracle(world):
         pytest.skip("needs %d GPUs" % world)
     counts = [1, 33, 4097, 100000, 1 << 20, (1 << 22) + 12345]
     run_ranks(_worker, world, args=(counts, 1e-4))
+
+
+def _raw_worker(rank, world):
+    import torch.distributed as dist
+
+    from datasets import gradient_like
+    from tirocinio_triennale_b200.parallel import CompressedAllreduce, collectives
+
+    n = 300_003
+    ar = CompressedAllreduce(n, timeout_ms=5000)
+    bufs = [gradient_like(n, seed=r) for r in range(world)]
+    x = torch.from_numpy(bufs[rank]).cuda()
+    for it in range(3):
+        out = torch.zeros_like(x)
+        collectives.allreduce_ring_gpu(ar, x, out)
+        want = torch.zeros(n)
+        for b in bufs:  # rank order, fp32: the kernel's summation order
+            want += torch.from_numpy(b)
+        assert ar.status() == 0
+        torch.testing.assert_close(out.cpu(), want, rtol=0, atol=0)
+    out2 = torch.zeros_like(x)
+    collectives.mixed_compressed_allreduce(ar, x, out2, 1e-4)
+    torch.testing.assert_close(out2.cpu(), want, rtol=0, atol=0)
+    # host-staged variant: same numbers as the device ring
+    out3 = torch.zeros_like(x)
+    collectives.cpuCopy_allreduce_ring_comprs_hom_sum_F(x, out3, 1e-4)
+    out4 = torch.zeros_like(x)
+    collectives.allreduce_ring_comprs_hom_sum_F_opt(ar, x, out4, 1e-4)
+    torch.testing.assert_close(out3, out4, rtol=0, atol=0)
+    dist.barrier()
+    ar.close()
+
+
+def test_uncompressed_and_named_variants():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    run_ranks(_raw_worker, 2)

@@ -74,6 +74,17 @@ class CompressedAllreduce:
                                              torch.cuda.current_stream().cuda_stream), "allreduce")
         return recv
 
+    def allreduce_raw(self, send: torch.Tensor, recv: torch.Tensor | None = None) -> torch.Tensor:
+        """Uncompressed sum with the library's own peer-memory kernels (bit-identical on all ranks)."""
+        if send.dtype != torch.float32 or not send.is_cuda or not send.is_contiguous():
+            raise ValueError("expected a contiguous float32 CUDA tensor")
+        if recv is None:
+            recv = send
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.hc_allreduce_raw(self._h, send.data_ptr(), recv.data_ptr(), send.numel(),
+                                                 torch.cuda.current_stream().cuda_stream), "allreduce_raw")
+        return recv
+
     def status(self, clear: bool = True) -> int:
         with torch.cuda.device(self.device):
             return int(self.lib.hc_comm_status(self._h, 1 if clear else 0))
