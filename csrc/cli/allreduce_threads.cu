@@ -1,0 +1,113 @@
+// Multi-GPU allreduce driver without Python, MPI or NCCL: one host thread per GPU of this machine,
+// peer access between all of them, the reference-named collective API (homcomp_compat.h).  Every
+// rank holds the same data, so the expected result is world * input; the check is the
+// reference checker's rule |world * in - out| <= 2 eb (world + world / 10)
+// (HomComp/src/utils/checksmooth.c:50-51).  Prints device-timed latency per mode.
+//
+//   allreduce_threads [gpus] [count] [eb] [iterations]
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include <atomic>
+#include <thread>
+#include <vector>
+
+#include "homcomp_compat.h"
+
+struct Barrier {
+  std::atomic<int> count{0}, sense{0};
+  int n;
+  explicit Barrier(int n_) : n(n_) {}
+  void wait(int& local) {
+    local ^= 1;
+    if (count.fetch_add(1) == n - 1) {
+      count.store(0);
+      sense.store(local);
+    } else {
+      while (sense.load() != local) std::this_thread::yield();
+    }
+  }
+};
+
+int main(int argc, char** argv) {
+  int ndev = 0;
+  cudaGetDeviceCount(&ndev);
+  int P = argc > 1 ? atoi(argv[1]) : ndev;
+  const size_t count = argc > 2 ? (size_t)atoll(argv[2]) : (size_t)1 << 22;
+  const float eb = argc > 3 ? (float)atof(argv[3]) : 1e-4f;
+  const int iters = argc > 4 ? atoi(argv[4]) : 10;
+  if (P < 1 || P > ndev || P > 8) {
+    fprintf(stderr, "need 1..%d GPUs\n", ndev < 8 ? ndev : 8);
+    return 2;
+  }
+  std::vector<float> host(count);
+  for (size_t i = 0; i < count; ++i) host[i] = (float)(sin(i * 3e-5) + 0.1 * sin(i * 7e-3));
+  const size_t sym = hc_comm_symmetric_bytes(P, count);
+  std::vector<void*> region(P, nullptr);
+  std::vector<int> failures(P, 0);
+  std::vector<float> lat_c(P, 0), lat_r(P, 0);
+  Barrier bar(P);
+  auto worker = [&](int r) {
+    int sense = 0;
+    cudaSetDevice(r);
+    for (int q = 0; q < P; ++q)
+      if (q != r) cudaDeviceEnablePeerAccess(q, 0);
+    cudaMalloc(&region[r], sym);
+    cudaMemset(region[r], 0, sym);
+    cudaDeviceSynchronize();
+    bar.wait(sense);
+    hc_comm* comm = nullptr;
+    if (hc_comm_create(&comm, r, P, count, region.data(), nullptr) != 0) { failures[r] = 1; return; }
+    float *d_in, *d_out;
+    cudaMalloc(&d_in, count * 4);
+    cudaMalloc(&d_out, count * 4);
+    cudaMemcpy(d_in, host.data(), count * 4, cudaMemcpyHostToDevice);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    std::vector<float> out(count);
+    for (int mode = 0; mode < 2; ++mode) {
+      float total = 0, ms;
+      for (int it = 0; it < iters + 2; ++it) {
+        bar.wait(sense);
+        cudaEventRecord(e0);
+        int rc = mode == 0 ? allreduce_ring_comprs_hom_sum_F(d_in, d_out, count, comm, eb)
+                           : allreduce_ring_gpu(d_in, d_out, count, comm);
+        cudaEventRecord(e1);
+        cudaEventSynchronize(e1);
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (rc) failures[r] = 1;
+        if (it >= 2) total += ms;
+      }
+      (mode == 0 ? lat_c : lat_r)[r] = total / iters;
+      cudaMemcpy(out.data(), d_out, count * 4, cudaMemcpyDeviceToHost);
+      const double tol = mode == 0 ? 2.0 * eb * (P + P / 10.0) : 1e-5 * P;
+      size_t bad = 0;
+      for (size_t i = 0; i < count; ++i)
+        if (fabs((double)host[i] * P - out[i]) > tol) ++bad;
+      if (bad || hc_comm_status(comm, 1) != 0) failures[r] = 1;
+      if (bad) fprintf(stderr, "rank %d mode %d: %zu values out of tolerance\n", r, mode, bad);
+    }
+    bar.wait(sense);
+    hc_comm_destroy(comm);
+    cudaFree(d_in);
+    cudaFree(d_out);
+    bar.wait(sense);
+    cudaFree(region[r]);
+  };
+  std::vector<std::thread> th;
+  for (int r = 0; r < P; ++r) th.emplace_back(worker, r);
+  for (auto& t : th) t.join();
+  float mc = 0, mr = 0;
+  int fail = 0;
+  for (int r = 0; r < P; ++r) {
+    mc = lat_c[r] > mc ? lat_c[r] : mc;
+    mr = lat_r[r] > mr ? lat_r[r] : mr;
+    fail |= failures[r];
+  }
+  printf("gpus %d count %zu eb %g | compressed allreduce %.3f ms (%.1f GB/s) | uncompressed %.3f ms (%.1f GB/s) | %s\n", P,
+         count, eb, mc, 4e-6 * count / mc, mr, 4e-6 * count / mr, fail ? "FAILED" : "ok");
+  return fail;
+}

@@ -1,0 +1,32 @@
+"""The native command-line tools (C++ against the reference-named API, no Python in the data path)."""
+import subprocess
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _tools():
+    from tirocinio_triennale_b200 import _build
+
+    return {p.name: p for p in _build.build_cli()}
+
+
+def test_homcomp_eval_tool():
+    exe = _tools()["homcomp_eval"]
+    r = subprocess.run([str(exe), "gen:3000000", "1e-4", "ABS", "3"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    line = [l for l in r.stdout.splitlines() if l.startswith("max abs err")][0]
+    err = float(line.split()[3])
+    assert err <= 2e-4 * 1.01  # two quantisation errors
+    assert "status no error" in r.stdout
+
+
+@pytest.mark.multigpu
+def test_allreduce_threads_tool():
+    n = min(torch.cuda.device_count(), 8)
+    exe = _tools()["allreduce_threads"]
+    r = subprocess.run([str(exe), str(n), "2000000", "1e-4", "3"], capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert r.stdout.strip().endswith("ok")

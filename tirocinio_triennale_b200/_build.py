@@ -102,6 +102,27 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
     return lib
 
 
+CLI_SOURCES = ["cli/homcomp_eval.cu", "cli/allreduce_threads.cu"]
+BINDIR = Path(__file__).resolve().parent / "bin"
+
+
+def build_cli(force: bool = False):
+    """Native command-line tools linked against libhomcomp_b200.so (rpath to the in-tree lib)."""
+    lib = build_cuda()
+    nvcc = nvcc_path()
+    BINDIR.mkdir(parents=True, exist_ok=True)
+    outs = []
+    for src in CLI_SOURCES:
+        exe = BINDIR / Path(src).stem
+        s = CSRC / src
+        if force or not exe.exists() or exe.stat().st_mtime < max(s.stat().st_mtime, lib.stat().st_mtime):
+            _run([nvcc, *NVCC_FLAGS, "-I", str(CSRC / "include"), str(s), "-o", str(exe), "-L", str(LIBDIR),
+                  "-lhomcomp_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../lib", "-lpthread"])
+        outs.append(exe)
+    return outs
+
+
 if __name__ == "__main__":
     print(build_cpu(force="--force" in sys.argv))
     print(build_cuda(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_cli(force="--force" in sys.argv))
