@@ -72,14 +72,16 @@ class ClockSampler:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
                  "-lms", str(self.period_ms)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
-            time.sleep(0.25)
+            t0 = time.time()
+            while os.path.getsize(self.path) == 0 and time.time() - t0 < 5.0:  # first sample is in
+                time.sleep(0.05)
         except Exception:
             self.proc = None
         return self
 
     def __exit__(self, *exc):
         if self.proc is not None:
-            time.sleep(0.15)
+            time.sleep(2.5 * self.period_ms / 1000.0)  # at least one more sample after the region
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
