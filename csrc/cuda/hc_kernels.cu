@@ -60,29 +60,40 @@ __device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, con
   return false;
 }
 
-// Loader-warp work for one input stream: rate bytes -> per-block offsets -> look-back -> one bulk
-// copy of the tile's payload bytes into `cbuf` (16-byte phase preserved).  Arrives on `full`.
+// Loader-warp work for one input stream, in two parts so that the rate bytes of the NEXT tile are
+// already in flight while the look-back of the current one polls:
+//   loader_fetch_rates   issues the loads of the tile's 128 rate bytes (4 per lane);
+//   loader_stage_stream  per-block offsets -> tile aggregate published -> look-back -> (wait until
+//                        the staging buffer is free) -> meta to shared memory -> one bulk copy of
+//                        the tile's payload bytes into `cbuf` (16-byte phase preserved); arrives on
+//                        `full`.
+// The aggregate is published before the wait for the buffer, so a ticket never sits without its
+// aggregate while this CTA's compute warps are busy.
+constexpr int kRatesPerLane = kTileBlocks / 32;
+__device__ __forceinline__ void loader_fetch_rates(const uint8_t* in, uint64_t in_size, uint32_t tile,
+                                                   uint32_t (&rate)[kRatesPerLane]) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t b0 = (uint64_t)tile * kTileBlocks + (uint64_t)lane * kRatesPerLane;
+#pragma unroll
+  for (int k = 0; k < kRatesPerLane; ++k) rate[k] = (b0 + k < in_size) ? ld_cg_u8(in + b0 + k) : 0u;
+}
+
 __device__ __forceinline__ void loader_stage_stream(const uint8_t* in, uint64_t in_size, uint64_t nrate, uint32_t tile,
                                                     const Chain& st, const Workspace& ws, uint8_t* cbuf, uint64_t* full,
-                                                    uint16_t* s_rel, uint8_t* s_rate, uint32_t* s_phase, bool usable) {
+                                                    uint16_t* s_rel, uint8_t* s_rate, uint32_t* s_phase, bool usable,
+                                                    const uint32_t (&rate_in)[kRatesPerLane], uint64_t* free_bar,
+                                                    uint32_t free_parity, bool wait_free, volatile uint32_t* abort) {
   const int lane = threadIdx.x & 31;
-  constexpr int kPer = kTileBlocks / 32;  // blocks per lane
+  constexpr int kPer = kRatesPerLane;
   uint32_t rate[kPer], len[kPer], sum = 0;
-  const uint64_t b0 = (uint64_t)tile * kTileBlocks + (uint64_t)lane * kPer;
 #pragma unroll
   for (int k = 0; k < kPer; ++k) {
-    rate[k] = (usable && b0 + k < in_size) ? ld_cg_u8(in + b0 + k) : 0u;
+    rate[k] = usable ? rate_in[k] : 0u;
     len[k] = payload_len(rate[k]);
     sum += len[k];
   }
   const uint32_t inc = warp_inclusive_scan(sum, lane);
   const uint32_t tot = __shfl_sync(0xffffffffu, inc, 31);
-  uint32_t rel = inc - sum;
-#pragma unroll
-  for (int k = 0; k < kPer; ++k) {
-    s_rel[lane * kPer + k] = (uint16_t)rel;
-    rel += len[k];
-  }
   bool ok;
   const uint64_t excl = lookback(st, tile, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
   ok = ok && usable;
@@ -91,8 +102,15 @@ __device__ __forceinline__ void loader_stage_stream(const uint8_t* in, uint64_t 
     if (lane == 0) note_error(ws.ctrl, kErrTruncated);
     ok = false;
   }
+  // the staging buffer (bytes and meta) is free once the compute threads have decoded its previous tile
+  if (wait_free && !wait_or_flag(free_bar, free_parity, ws, abort)) ok = false;
+  uint32_t rel = inc - sum;
 #pragma unroll
-  for (int k = 0; k < kPer; ++k) s_rate[lane * kPer + k] = ok ? (uint8_t)rate[k] : (uint8_t)0;
+  for (int k = 0; k < kPer; ++k) {
+    s_rel[lane * kPer + k] = (uint16_t)rel;
+    s_rate[lane * kPer + k] = ok ? (uint8_t)rate[k] : (uint8_t)0;
+    rel += len[k];
+  }
   const uint8_t* src = in + base;
   const uint32_t phase = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 15u);
   if (lane == 0) *s_phase = phase;
@@ -107,6 +125,22 @@ __device__ __forceinline__ void loader_stage_stream(const uint8_t* in, uint64_t 
       mbar_arrive(full);
     }
   }
+}
+
+// ring steps: has the tile's arrival flag been raised yet? (one non-blocking look)
+__device__ __forceinline__ bool flag_is_up(const uint32_t* flag, uint32_t want) {
+  uint32_t up = 0;
+  if ((threadIdx.x & 31) == 0) up = ld_acquire_sys_u32(flag) == want ? 1u : 0u;
+  return __shfl_sync(0xffffffffu, up, 0) != 0;
+}
+// ring steps: bounded wait for the tile's arrival flag; false = the peer never delivered
+__device__ __forceinline__ bool flag_wait_warp(const uint32_t* flag, uint32_t want, const Workspace& ws) {
+  uint32_t okf = 1;
+  if ((threadIdx.x & 31) == 0) {
+    okf = wait_flag(flag, want, ws.spin_limit_ns, ws.ctrl + 2) ? 1u : 0u;
+    if (!okf) note_error(ws.ctrl, kErrPeer);
+  }
+  return __shfl_sync(0xffffffffu, okf, 0) != 0;
 }
 
 // Shared-memory plan of the stream-producing kernel (offsets from a 1024-byte aligned base):
@@ -185,50 +219,65 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
 
   if (warp == kComputeThreads / 32) {
     // ================================ loader warp ================================================
-    // tickets are taken one turn ahead so the atomic's round trip is off the refill path
-    uint32_t next_tile = kNoTile;
-    if (lane == 0 && !*abort) next_tile = atomicAdd(ws.ctrl, 1u);
+    // Software pipeline over this CTA's tiles: the ticket is taken two turns ahead and the input
+    // stream's rate bytes one turn ahead, so neither round trip sits between two look-backs.  Per
+    // tile: input stream first (its aggregate is published before any wait on this CTA's compute
+    // warps), then the fp32 tile's TMA load once its stage is free.
+    auto take = [&]() -> uint32_t {
+      uint32_t t = kNoTile;
+      if (lane == 0 && !*abort) t = atomicAdd(ws.ctrl, 1u);
+      t = __shfl_sync(0xffffffffu, t, 0);
+      return t < p.n_tiles ? t : kNoTile;
+    };
+    auto try_fetch = [&](uint32_t t, uint32_t (&r)[kRatesPerLane]) -> bool {  // non-blocking
+      if (!kHasIn || kStreams != 1 || t == kNoTile) return false;
+      if (p.in_ready && !flag_is_up(p.in_ready + t, p.ring_epoch)) return false;
+      loader_fetch_rates(p.in, p.in_size, t, r);
+      return true;
+    };
+    uint32_t tile = take();
+    uint32_t tile_n = tile != kNoTile ? take() : kNoTile;
+    uint32_t rates[kRatesPerLane] = {}, rates_n[kRatesPerLane] = {};
+    bool have = try_fetch(tile, rates), have_n = false;
     for (uint32_t k = 0;; ++k) {
       const int s = k % NS, slot = k & 7;
-      uint32_t tile = __shfl_sync(0xffffffffu, next_tile, 0);
-      if (tile >= p.n_tiles) tile = kNoTile;
-      if (tile != kNoTile && lane == 0) next_tile = *abort ? kNoTile : atomicAdd(ws.ctrl, 1u);
-      // stage s is free once the tile packed there NS turns ago has been moved out
-      if (k >= NS && !wait_or_flag(&sh.stage_free[s], ((k / NS) - 1) & 1, ws, abort)) tile = kNoTile;
-      if (lane == 0) {
-        sh.tile[slot] = tile;
-        const bool fetch = tma && tile != kNoTile && (uint64_t)tile * kTileBlocks < full_rows;
-        sh.tile_tma[slot] = fetch ? 1u : 0u;
-        if (fetch) {
-          fence_proxy_async();
-          mbar_expect_tx(&sh.tma_full[s], kTileBytes);
-          tma_load_2d(stage0 + s * kStagePitch, &tmap, 0, (int)(tile * kTileBlocks), &sh.tma_full[s]);
-        } else {
-          mbar_arrive(&sh.tma_full[s]);
-        }
-      }
-      if (tile == kNoTile) break;
-      if (kHasIn) {
+      const uint32_t tile_nn = (tile != kNoTile && tile_n != kNoTile) ? take() : kNoTile;
+      if (tile != kNoTile) have_n = try_fetch(tile_n, rates_n);
+      if (kHasIn && tile != kNoTile) {
         bool usable = true;
-        if (p.in_ready) {
-          uint32_t okf = 1;
-          if (lane == 0) okf = wait_flag(p.in_ready + tile, p.ring_epoch, ws.spin_limit_ns, ws.ctrl + 2) ? 1u : 0u;
-          okf = __shfl_sync(0xffffffffu, okf, 0);
-          if (!okf) {
-            if (lane == 0) note_error(ws.ctrl, kErrPeer);
-            usable = false;
-          }
-        }
+        if (p.in_ready && !have && !flag_wait_warp(p.in_ready + tile, p.ring_epoch, ws)) usable = false;
 #pragma unroll
         for (int q = 0; q < kStreams; ++q) {
           const int b = in_buf(k, q);
           const uint32_t u = in_use(k);
-          // the buffer is free once the compute threads have decoded its previous tile
-          if (u >= 1 && !wait_or_flag(&sh.in_free[b], (u - 1) & 1, ws, abort)) usable = false;
-          loader_stage_stream(q ? p.in2 : p.in, q ? p.in2_size : p.in_size, nrate, tile, q ? Chain{ws.st_b, ws.grp_b} : Chain{ws.st_a, ws.grp_a}, ws,
-                              cbuf[b], &sh.in_full[b], sh.in_rel[b], sh.in_rate[b], &sh.in_phase[b], usable);
+          if (!(q == 0 && have) && usable) loader_fetch_rates(q ? p.in2 : p.in, q ? p.in2_size : p.in_size, tile, rates);
+          loader_stage_stream(q ? p.in2 : p.in, q ? p.in2_size : p.in_size, nrate, tile,
+                              q ? Chain{ws.st_b, ws.grp_b} : Chain{ws.st_a, ws.grp_a}, ws, cbuf[b], &sh.in_full[b],
+                              sh.in_rel[b], sh.in_rate[b], &sh.in_phase[b], usable, rates, &sh.in_free[b], (u - 1) & 1,
+                              u >= 1, abort);
         }
       }
+      // stage s is free once the tile packed there NS turns ago has been moved out
+      uint32_t t_stage = tile;
+      if (k >= NS && !wait_or_flag(&sh.stage_free[s], ((k / NS) - 1) & 1, ws, abort)) t_stage = kNoTile;
+      if (lane == 0) {
+        sh.tile[slot] = t_stage;
+        const bool fetch = tma && t_stage != kNoTile && (uint64_t)t_stage * kTileBlocks < full_rows;
+        sh.tile_tma[slot] = fetch ? 1u : 0u;
+        if (fetch) {
+          fence_proxy_async();
+          mbar_expect_tx(&sh.tma_full[s], kTileBytes);
+          tma_load_2d(stage0 + s * kStagePitch, &tmap, 0, (int)(t_stage * kTileBlocks), &sh.tma_full[s]);
+        } else {
+          mbar_arrive(&sh.tma_full[s]);
+        }
+      }
+      if (t_stage == kNoTile) break;
+      tile = tile_n;
+      tile_n = tile_nn;
+      have = have_n;
+#pragma unroll
+      for (int i = 0; i < kRatesPerLane; ++i) rates[i] = rates_n[i];
     }
   } else if (warp == kComputeThreads / 32 + 1) {
     // ================================ scanner warp ===============================================
@@ -375,13 +424,15 @@ struct __align__(16) DecShared {
 };
 
 template <int MODE>
-__global__ void __launch_bounds__(kDecThreads, 3)
+__global__ void __launch_bounds__(kDecThreads, 4)
 hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ DecShared sh;
-  uint8_t* obuf[2] = {smem, smem + kTileBytes};
-  uint8_t* cbuf[2] = {smem + 2 * kTileBytes, smem + 2 * kTileBytes + kBufBytes};
+  // one output tile (its TMA store has a whole tile time to read it out) + two staging buffers:
+  // 51 KB per CTA, four CTAs per SM
+  uint8_t* const obuf = smem;
+  uint8_t* cbuf[2] = {smem + kTileBytes, smem + kTileBytes + kBufBytes};
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -403,36 +454,56 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
 
   if (warp == kComputeThreads / 32) {
     // ================================ loader warp ================================================
-    uint32_t next_tile = kNoTile;
-    if (lane == 0 && !*abort) next_tile = atomicAdd(ws.ctrl, 1u);
+    // Software pipeline over this CTA's tiles: the ticket is taken two turns ahead and the rate
+    // bytes one turn ahead, so neither round trip sits between two look-backs.
+    auto take = [&]() -> uint32_t {  // lane 0 takes a ticket, every lane gets it
+      uint32_t t = kNoTile;
+      if (lane == 0 && !*abort) t = atomicAdd(ws.ctrl, 1u);
+      t = __shfl_sync(0xffffffffu, t, 0);
+      return t < p.n_tiles ? t : kNoTile;
+    };
+    auto try_fetch = [&](uint32_t t, uint32_t (&r)[kRatesPerLane]) -> bool {  // non-blocking
+      if (t == kNoTile) return false;
+      const uint32_t sg = t / p.tiles_per_seg, lt = t - sg * p.tiles_per_seg;
+      const DecSegment& seg = p.seg[sg];
+      if (seg.in_ready && !flag_is_up(seg.in_ready + lt, p.ring_epoch)) return false;
+      loader_fetch_rates(seg.in, seg.in_size, lt, r);
+      return true;
+    };
+    uint32_t tile = take();
+    uint32_t tile_n = tile != kNoTile ? take() : kNoTile;
+    uint32_t rates[kRatesPerLane] = {}, rates_n[kRatesPerLane] = {};
+    bool have = try_fetch(tile, rates), have_n = false;
     for (uint32_t k = 0;; ++k) {
       const int s = k & 1;
-      uint32_t tile = __shfl_sync(0xffffffffu, next_tile, 0);
-      if (tile >= p.n_tiles) tile = kNoTile;
-      if (tile != kNoTile && lane == 0) next_tile = *abort ? kNoTile : atomicAdd(ws.ctrl, 1u);
-      if (k >= 2 && !wait_or_flag(&sh.in_free[s], ((k >> 1) - 1) & 1, ws, abort)) tile = kNoTile;
-      if (lane == 0) sh.tile[k & 3] = tile;
       if (tile == kNoTile) {
+        // end marker; the buffer's previous phase must have been consumed before it is re-armed
+        if (k >= 2) wait_or_flag(&sh.in_free[s], ((k >> 1) - 1) & 1, ws, abort);
+        if (lane == 0) sh.tile[k & 3] = kNoTile;
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh.in_full[s]);
         break;
       }
+      const uint32_t tile_nn = tile_n != kNoTile ? take() : kNoTile;
+      have_n = try_fetch(tile_n, rates_n);
       const uint32_t sg = tile / p.tiles_per_seg, lt = tile - sg * p.tiles_per_seg;
       const DecSegment& seg = p.seg[sg];
       bool usable = true;
-      if (seg.in_ready) {
-        uint32_t okf = 1;
-        if (lane == 0) okf = wait_flag(seg.in_ready + lt, p.ring_epoch, ws.spin_limit_ns, ws.ctrl + 2) ? 1u : 0u;
-        okf = __shfl_sync(0xffffffffu, okf, 0);
-        if (!okf) {
-          if (lane == 0) note_error(ws.ctrl, kErrPeer);
-          usable = false;
-        }
+      if (!have) {
+        if (seg.in_ready && !flag_wait_warp(seg.in_ready + lt, p.ring_epoch, ws)) usable = false;
+        if (usable) loader_fetch_rates(seg.in, seg.in_size, lt, rates);
       }
       const Chain chain{ws.st_a + (size_t)sg * p.tiles_per_seg, ws.grp_a + (size_t)sg * groups_per_seg};
+      if (lane == 0) sh.tile[k & 3] = tile;  // ring of 4 > 2 buffers: nobody still reads this slot
       loader_stage_stream(seg.in, seg.in_size, rate_bytes(seg.n), lt, chain, ws, cbuf[s], &sh.in_full[s], sh.in_rel[s],
-                          sh.in_rate[s], &sh.in_phase[s], usable);
+                          sh.in_rate[s], &sh.in_phase[s], usable, rates, &sh.in_free[s], ((k >> 1) - 1) & 1, k >= 2,
+                          abort);
       if (lane == 0 && fatal_error(ws.ctrl)) *abort = 1;
+      tile = tile_n;
+      tile_n = tile_nn;
+      have = have_n;
+#pragma unroll
+      for (int i = 0; i < kRatesPerLane; ++i) rates[i] = rates_n[i];
     }
   } else {
     // ================================ compute warps ==============================================
@@ -451,8 +522,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
       W = __reduce_max_sync(0xffffffffu, W);
       int32_t d[32];
       if (__any_sync(0xffffffffu, rate != 0)) {
-        decode_block(cbuf[s], pos, rate, W, d);
-        lorenzo_inverse<MODE>(d);
+        decode_block_quant<MODE>(cbuf[s], pos, rate, W, d);
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) d[i] = 0;
@@ -464,18 +534,17 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
 
       const uint64_t row = (uint64_t)lt * kTileBlocks + tid;
       const bool ragged = row * kBlock < seg.n && (row + 1) * kBlock > seg.n;
-      // the TMA store that used obuf[s] two tiles ago must have finished reading it (every turn
-      // commits exactly one group, empty when the tile goes out with plain stores)
-      if (tid == 0) tma_wait_group_read<1>();
+      // the TMA store of the previous tile must have finished reading obuf
+      if (tid == 0) tma_wait_group_read<0>();
       compute_barrier();
       if (tma) {
-        store_row_swizzled(obuf[s], tid, w);
+        store_row_swizzled(obuf, tid, w);
         fence_proxy_async();
       }
       compute_barrier();
       if (tid == 0) {
         if (tma && (uint64_t)lt * kTileBlocks < full_rows)
-          tma_store_2d(&tmaps.m[sg], 0, (int)(lt * kTileBlocks), obuf[s]);
+          tma_store_2d(&tmaps.m[sg], 0, (int)(lt * kTileBlocks), obuf);
         tma_commit_group();
       }
       if (!tma || ragged) {
@@ -593,7 +662,7 @@ DeviceInfo& device_info() {
 
 constexpr int kEncSmemLocalOnly = dev::enc_smem_base(kOpCompress) + 1024;
 constexpr int kEncSmemWithIn = dev::enc_smem_base(kOpAddF32) + 2 * kBufBytes + 1024;
-constexpr int kDecSmem = 2 * kTileBytes + 2 * kBufBytes + 1024;
+constexpr int kDecSmem = kTileBytes + 2 * kBufBytes + 1024;
 
 template <typename K>
 cudaError_t set_smem(K kernel, int bytes) {
@@ -706,7 +775,7 @@ cudaError_t launch_decode(int mode, DecParams p, cudaStream_t stream) {
   memset(&maps, 0, sizeof(maps));
   for (uint32_t i = 0; i < p.n_seg; ++i)
     p.seg[i].use_tma = make_rows_map(&maps.m[i], p.seg[i].out, p.seg[i].n / kBlock) ? 1u : 0u;
-  int grid = grid_for_tiles(p.n_tiles, 3);
+  int grid = grid_for_tiles(p.n_tiles, 4);
   switch (mode) {
     case kModeOutlier:
     case kModePlain: return launch_decode_t<kModeOutlier>(maps, p, grid, stream);

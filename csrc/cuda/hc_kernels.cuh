@@ -256,42 +256,57 @@ __device__ __forceinline__ void write_payload(uint8_t* obuf, uint32_t pos, const
 }
 
 // Reads the block's payload at byte `pos` of a staged stream; returns the sign map (memory form),
-// planes in T[0..W-1] (zero above F) and |d0| of an outlier block in a0.
+// planes in T[0..W-1] (zero at and above F) and |d0| of an outlier block in a0.  Word-aligned
+// blocks take predicated 32-bit loads; shifted ones rebuild every word from two neighbours.
 template <int W>
 __device__ __forceinline__ void read_payload_w(const uint8_t* cbuf, uint32_t pos, uint32_t rate, uint32_t& sign_mem,
                                                uint32_t& a0, uint32_t (&T)[32]) {
   const uint32_t F = rate & 31u;
   const bool outl = (rate & 0x80u) != 0;
-  const bool has = outl || F != 0;
-  const uint32_t nout = outl ? ((rate >> 5) & 3u) + 1u : 0u;
   a0 = 0;
-#pragma unroll
-  for (uint32_t k = 0; k < 4; ++k)
-    if (k < nout) a0 |= (uint32_t)cbuf[pos + k] << (8 * k);
-  const uint32_t p2 = pos + nout;
-  const uint32_t sh = 8u * (p2 & 3u);
-  const uint32_t* wp = reinterpret_cast<const uint32_t*>(cbuf + (p2 & ~3u));
-  uint32_t prev = has ? wp[0] : 0u;
   sign_mem = 0;
 #pragma unroll
-  for (int j = 0; j <= W; ++j) {
-    uint32_t nxt = (has && (uint32_t)j <= F) ? wp[j + 1] : 0u;
-    uint32_t x = __funnelshift_r(prev, nxt, sh);
-    if (j == 0) sign_mem = has ? x : 0u;
-    else T[j - 1 < 32 ? j - 1 : 31] = ((uint32_t)(j - 1) < F) ? x : 0u;
-    prev = nxt;
+  for (int j = 0; j < (W ? W : 1); ++j) T[j] = 0;
+  if (!outl && F == 0) return;
+  uint32_t p2 = pos;
+  if (outl) {
+    const uint32_t nout = ((rate >> 5) & 3u) + 1u;
+#pragma unroll
+    for (uint32_t k = 0; k < 4; ++k)
+      if (k < nout) a0 |= (uint32_t)cbuf[pos + k] << (8 * k);
+    p2 += nout;
+  }
+  const uint32_t s = p2 & 3u;
+  const uint32_t* wp = reinterpret_cast<const uint32_t*>(cbuf + (p2 & ~3u));
+  if (s == 0) {
+    sign_mem = wp[0];
+#pragma unroll
+    for (int j = 1; j <= W; ++j)
+      if ((uint32_t)j <= F) T[j - 1] = wp[j];
+  } else {
+    const uint32_t sh = 8u * s;
+    uint32_t prev = wp[0];
+#pragma unroll
+    for (int j = 0; j <= W; ++j) {
+      const bool live = (uint32_t)j <= F;
+      const uint32_t nxt = live ? wp[j + 1] : 0u;
+      const uint32_t x = __funnelshift_r(prev, nxt, sh);
+      if (j == 0) sign_mem = x;
+      else if (live) T[j - 1] = x;
+      prev = nxt;
+    }
   }
 }
 
-// staged payload -> signed deltas d[0..31]
-__device__ __forceinline__ void decode_block(const uint8_t* cbuf, uint32_t pos, uint32_t rate, int W, int32_t (&d)[32]) {
-  uint32_t T[32];
+// staged payload -> rows R[j] = |d[j ^ 7]| and the sign map in value form (element i at bit 31 - i)
+__device__ __forceinline__ uint32_t decode_magnitudes(const uint8_t* cbuf, uint32_t pos, uint32_t rate, int W,
+                                                      uint32_t (&T)[32]) {
   uint32_t sign_mem, a0;
   switch (W) {
     case 0:
+      read_payload_w<0>(cbuf, pos, rate, sign_mem, a0, T);
 #pragma unroll
       for (int i = 0; i < 32; ++i) T[i] = 0;
-      read_payload_w<0>(cbuf, pos, rate, sign_mem, a0, T);
       break;
     case 4: read_payload_w<4>(cbuf, pos, rate, sign_mem, a0, T); rows_from_planes<4>(T); break;
     case 8: read_payload_w<8>(cbuf, pos, rate, sign_mem, a0, T); rows_from_planes<8>(T); break;
@@ -299,11 +314,33 @@ __device__ __forceinline__ void decode_block(const uint8_t* cbuf, uint32_t pos, 
     default: read_payload_w<32>(cbuf, pos, rate, sign_mem, a0, T); rows_from_planes<32>(T); break;
   }
   if (rate & 0x80u) T[7] = a0 & 0x7fffffffu;
-  const uint32_t sign = __byte_perm(sign_mem, 0, 0x0123);
+  return __byte_perm(sign_mem, 0, 0x0123);
+}
+
+// staged payload -> signed deltas d[0..31]
+__device__ __forceinline__ void decode_block(const uint8_t* cbuf, uint32_t pos, uint32_t rate, int W, int32_t (&d)[32]) {
+  uint32_t T[32];
+  const uint32_t sign = decode_magnitudes(cbuf, pos, rate, W, T);
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
-    int32_t m = (int32_t)(sign << i) >> 31;
+    const int32_t m = (int32_t)(sign << i) >> 31;
     d[i] = ((int32_t)T[i ^ 7] ^ m) - m;
+  }
+}
+
+// staged payload -> quantised values q[0..31]: sign application and inverse Lorenzo in one pass
+// (q_i = q_{i-S} + (|d_i| ^ m_i) - m_i is a single three-input add per element)
+template <int MODE>
+__device__ __forceinline__ void decode_block_quant(const uint8_t* cbuf, uint32_t pos, uint32_t rate, int W,
+                                                   int32_t (&q)[32]) {
+  constexpr int S = MODE == kModeVec ? 4 : 1;
+  uint32_t T[32];
+  const uint32_t sign = decode_magnitudes(cbuf, pos, rate, W, T);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int32_t m = (int32_t)(sign << i) >> 31;
+    const int32_t t = (int32_t)T[i ^ 7] ^ m;
+    q[i] = i >= S ? q[i - S] + t - m : t - m;
   }
 }
 

@@ -71,6 +71,9 @@ struct hc_comm {
   uint32_t ws_epoch = 0;
   uint32_t call = 0;
   uint32_t raw_call = 0;
+  bool trace = false;             // record one CUDA event per step of hc_allreduce
+  cudaEvent_t ev[hc::kMaxDst + 3] = {};
+  int n_ev = 0;
   uint64_t spin_limit_ns = 2000ull * 1000 * 1000;
 };
 
@@ -117,12 +120,36 @@ int hc_comm_create(hc_comm** out, int rank, int world, size_t max_count, void* c
     hc_comm_destroy(c);
     return hc::kErrCuda;
   }
+  for (auto& e : c->ev)
+    if (cudaEventCreate(&e) != cudaSuccess) {
+      hc_comm_destroy(c);
+      return hc::kErrCuda;
+    }
   *out = c;
   return hc::kOk;
 }
 
+int hc_comm_set_trace(hc_comm* c, int on) {
+  if (!c) return hc::kErrArgument;
+  c->trace = on != 0;
+  return hc::kOk;
+}
+
+// device time of every step of the last traced hc_allreduce: ms[0..world-1] the reduce-scatter
+// steps, ms[world] the decode; returns the number of entries (synchronises the device)
+int hc_comm_last_step_ms(hc_comm* c, float* ms, int n) {
+  if (!c || !ms) return 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return 0;
+  int k = 0;
+  for (; k + 1 < c->n_ev && k < n; ++k)
+    if (cudaEventElapsedTime(&ms[k], c->ev[k], c->ev[k + 1]) != cudaSuccess) break;
+  return k;
+}
+
 void hc_comm_destroy(hc_comm* c) {
   if (!c) return;
+  for (auto& e : c->ev)
+    if (e) cudaEventDestroy(e);
   if (c->ws_mem) cudaFree(c->ws_mem);
   if (c->sizes) cudaFree(c->sizes);
   delete c;
@@ -170,6 +197,11 @@ int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, f
   const int next = (r + 1) % P;
   uint8_t* self = c->peer[r];
 
+  c->n_ev = 0;
+  auto mark = [&]() {
+    if (c->trace) cudaEventRecord(c->ev[c->n_ev++], stream);
+  };
+  mark();
   // ---- reduce-scatter: steps 0 .. P-1 (the last one feeds the all-gather buffers) --------------
   for (int s = 0; s < P; ++s) {
     const int ch = ((r - s) % P + P) % P;
@@ -207,6 +239,7 @@ int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, f
     p.ws = next_ws(c, stream);
     if (hc::launch_encode(s == 0 ? hc::kOpCompress : hc::kOpAddF32, hc::kModeOutlier, p, stream) != cudaSuccess)
       return hc::kErrCuda;
+    mark();
   }
 
   // ---- all-gather side: one kernel decodes the P reduced chunks as their tiles arrive ------------
@@ -229,6 +262,7 @@ int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, f
   }
   d.ws = next_ws(c, stream);
   if (hc::launch_decode(hc::kModeOutlier, d, stream) != cudaSuccess) return hc::kErrCuda;
+  mark();
   return hc::kOk;
 }
 

@@ -104,6 +104,10 @@ int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, f
 // Uncompressed sum over the same peer mappings (two-shot direct algorithm, three kernels); the
 // compressed and the uncompressed collective of one handle must not be in flight together.
 int hc_allreduce_raw(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, hc_stream_t stream);
+// Tracing: with trace on, hc_allreduce records one CUDA event per step; hc_comm_last_step_ms returns
+// the device time of each step of the last call (reduce-scatter steps, then the decode).
+int hc_comm_set_trace(hc_comm* c, int on);
+int hc_comm_last_step_ms(hc_comm* c, float* ms, int n);
 // device-side counters of the last call: bytes[s] = stream bytes this rank produced at step s
 int hc_comm_last_stream_bytes(hc_comm* c, uint64_t* bytes, int n);
 

@@ -89,6 +89,17 @@ class CompressedAllreduce:
         with torch.cuda.device(self.device):
             return int(self.lib.hc_comm_status(self._h, 1 if clear else 0))
 
+    def set_trace(self, on: bool = True):
+        """Record one CUDA event per step of every following allreduce (see ``last_step_ms``)."""
+        _lib.check(self.lib.hc_comm_set_trace(self._h, 1 if on else 0), "set_trace")
+
+    def last_step_ms(self):
+        """Device time of each step of the last traced call: reduce-scatter steps, then the decode."""
+        arr = (C.c_float * 16)()
+        with torch.cuda.device(self.device):
+            n = int(self.lib.hc_comm_last_step_ms(self._h, arr, 16))
+        return list(arr)[:n]
+
     def last_stream_bytes(self):
         """Stream bytes this rank produced at each step of the last call (synchronises)."""
         arr = (C.c_uint64 * 16)()
