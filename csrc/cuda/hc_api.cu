@@ -141,8 +141,8 @@ int hc_hom_add_stream(hc_codec* c, const uint8_t* d_a, size_t a_size, const uint
   return encode_call(c, hc::kOpAddStream, mode, nullptr, d_a, a_size, d_b, b_size, n, 1.0f, d_out, cap, d_size, stream);
 }
 
-int hc_decompress(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, float eb, int mode, float* d_x,
-                  hc_stream_t stream) {
+static int decompress_call(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, float eb, int mode, float* d_x,
+                           const uint32_t* d_tile_flags, uint32_t want, hc_stream_t stream) {
   if (int rc = check_call(c, n, eb, true)) return rc;
   if (mode < 0 || mode > 2 || !d_in || !d_x) return hc::kErrArgument;
   if (n == 0) return hc::kOk;
@@ -151,12 +151,27 @@ int hc_decompress(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, fl
   p.n_seg = 1;
   p.seg[0].in = d_in;
   p.seg[0].in_size = in_size;
+  p.seg[0].in_ready = d_tile_flags;
   p.seg[0].out = d_x;
   p.seg[0].n = n;
+  p.ring_epoch = want;
   p.eb = eb;
   p.ws = next_workspace(c, stream);
   return hc::launch_decode(mode, p, stream) == cudaSuccess ? hc::kOk : hc::kErrCuda;
 }
+
+int hc_decompress(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, float eb, int mode, float* d_x,
+                  hc_stream_t stream) {
+  return decompress_call(c, d_in, in_size, n, eb, mode, d_x, nullptr, 0, stream);
+}
+
+int hc_decompress_flagged(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, float eb, int mode, float* d_x,
+                          const uint32_t* d_tile_flags, uint32_t want, hc_stream_t stream) {
+  if (!d_tile_flags) return hc::kErrArgument;
+  return decompress_call(c, d_in, in_size, n, eb, mode, d_x, d_tile_flags, want, stream);
+}
+
+size_t hc_tile_elems(void) { return hc::kTileElems; }
 
 int hc_quant_pred(const float* d_x, size_t n, float eb, int mode, int32_t* d_deltas, hc_stream_t stream) {
   if (!(eb > 0.0f) || !d_x || !d_deltas) return hc::kErrArgument;

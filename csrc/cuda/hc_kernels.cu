@@ -18,6 +18,7 @@ struct __align__(16) EncShared {
   uint64_t stage_free[kMaxStages];  // compute threads have moved the packed tile out of stage s
   uint64_t scan_done[kMaxStages];   // tile total known: the scanner may start its look-back
   uint64_t base_ready[kMaxStages];  // look-back of the tile in stage s finished: out_base / out_ok valid
+  uint64_t moved[kMaxStages];       // compute threads have stored the tile of stage s to its destinations
   uint64_t in_full[2];              // input stream bytes + meta staged in buffer b
   uint64_t in_free[2];              // compute threads have decoded from buffer b
   uint32_t tile[8];                 // ring of tile tickets, written by the loader
@@ -182,6 +183,7 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
       mbar_init(&sh.stage_free[i], kComputeThreads);
       mbar_init(&sh.scan_done[i], 1);
       mbar_init(&sh.base_ready[i], 1);
+      mbar_init(&sh.moved[i], kComputeThreads);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sh.in_full[i], 1);
@@ -202,14 +204,21 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
     const uint32_t tile = sh.tile[j & 7];
     const bool ok = sh.out_ok[sj] != 0;
     if (ok) copy_out(stage0 + sj * kStagePitch, p.out, p.n_dst, sh.out_base[sj], sh.out_tot[sj], tid, kComputeThreads);
-    if (p.out_ready[0] != nullptr) {  // a step of a collective: tell the consumers the tile has landed
-      compute_barrier();
-      if ((uint32_t)tid < p.n_dst && p.out_ready[tid] != nullptr) {
-        __threadfence_system();
-        st_release_sys_u32(p.out_ready[tid] + tile, ok ? p.ring_epoch : 0xffffffffu);
-      }
+    (void)tile;
+    mbar_arrive(&sh.moved[sj]);       // the scanner raises the consumers' arrival flags (ring steps)
+    mbar_arrive(&sh.stage_free[sj]);  // the loader may refill the stage
+  };
+  // scanner warp, ring steps only: once the compute threads have stored tile j of this CTA, fence
+  // at system scope and raise the tile's arrival flag on every destination.  Doing this here keeps
+  // the system fence (a round trip to the peers) off the compute warps.
+  auto raise_flags = [&](uint32_t j) {
+    const int sj = j % NS;
+    if (!wait_or_flag(&sh.moved[sj], (j / NS) & 1, ws, abort)) return;
+    if ((uint32_t)lane < p.n_dst && p.out_ready[lane] != nullptr) {
+      __threadfence_system();
+      st_release_sys_u32(p.out_ready[lane] + sh.tile[j & 7], sh.out_ok[sj] ? p.ring_epoch : 0xffffffffu);
     }
-    mbar_arrive(&sh.stage_free[sj]);
+    __syncwarp();
   };
 
   // One input stream: its staging buffer alternates with the tile counter (buffer k & 1, use k >> 1).
@@ -283,12 +292,16 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
     // ================================ scanner warp ===============================================
     // runs the decoupled look-back of the output stream as soon as a tile's total is known, while
     // the compute warps are still transposing and packing; hands them the tile's global offset
+    const bool ring = p.out_ready[0] != nullptr;
     for (uint32_t k = 0;; ++k) {
       const int s = k % NS;
       const uint32_t par = (k / NS) & 1;
       if (!wait_or_flag(&sh.scan_done[s], par, ws, abort)) break;
       const uint32_t tile = sh.tile[k & 7];
-      if (tile == kNoTile) break;
+      if (tile == kNoTile) {
+        if (ring && kLag && k >= 1) raise_flags(k - 1);  // the tile that left one turn late
+        break;
+      }
       const uint32_t tot = sh.out_tot[s];
       bool ok = true;
       const uint64_t excl = lookback(Chain{ws.st_out, ws.grp_out}, tile, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
@@ -304,6 +317,8 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
         if (ok && tile == p.n_tiles - 1 && p.size_out) *p.size_out = goff + tot;
         if (fatal_error(ws.ctrl)) *abort = 1;
       }
+      __syncwarp();
+      if (ring && k >= (uint32_t)kLag) raise_flags(k - kLag);
     }
   } else {
     // ================================ compute warps ==============================================

@@ -71,6 +71,13 @@ int hc_compress(hc_codec* c, const float* d_x, size_t n, float eb, int mode, uin
                 uint64_t* d_size, hc_stream_t stream);
 int hc_decompress(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, float eb, int mode, float* d_x,
                   hc_stream_t stream);
+// Streaming decode: the stream is being written by another producer (another stream, another GPU);
+// d_tile_flags holds one uint32 per tile of hc_tile_elems() values, and tile t is decoded once
+// d_tile_flags[t] == want (acquire at system scope).  A flag that never rises ends in status 6
+// (peer) after the handle's timeout; the kernel always runs to its end.
+int hc_decompress_flagged(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, float eb, int mode, float* d_x,
+                          const uint32_t* d_tile_flags, uint32_t want, hc_stream_t stream);
+size_t hc_tile_elems(void);
 int hc_hom_add_f32(hc_codec* c, const uint8_t* d_in, size_t in_size, const float* d_local, size_t n, float eb,
                    int mode, uint8_t* d_out, size_t cap, uint64_t* d_size, hc_stream_t stream);
 // d_deltas: hc_quant_pred output, padded to whole 32-element blocks

@@ -1,0 +1,49 @@
+"""Failure detection on the device without faulting it: every wait is bounded, a wait that runs
+out ends in a status word that the host reads, and the context stays usable."""
+import time
+
+import numpy as np
+import pytest
+import torch
+
+from tirocinio_triennale_b200 import ops
+
+pytestmark = pytest.mark.gpu
+
+
+def test_flag_that_never_rises_times_out_with_status():
+    n, eb = 100_000, 1e-4
+    x = np.random.default_rng(0).normal(0, 0.01, n).astype(np.float32)
+    s = ops.cpu_compress(x, eb)
+    gs = torch.from_numpy(np.concatenate([s, np.zeros(64, np.uint8)])).cuda()
+    codec = ops.Codec(n, timeout_ms=300)
+    tiles = (ops.rate_bytes(n) * 32) // codec.tile_elems
+    flags = torch.zeros(tiles, dtype=torch.int32, device="cuda")
+    # producer "arrived" for the first tiles only; nothing ever sets the rest
+    flags[:3] = 7
+    t0 = time.time()
+    y = codec.decompress_flagged(gs, n, eb, flags, want=7, stream_bytes=s.size)
+    status = codec.status()
+    assert status == 6  # peer never delivered
+    assert time.time() - t0 < 20  # bounded, not a hang
+    want = ops.cpu_decompress(s, n, eb)
+    done = 3 * codec.tile_elems
+    np.testing.assert_array_equal(y[:done].cpu().numpy(), want[:done])  # delivered tiles were decoded
+    # all flags up: the same handle works again
+    flags.fill_(9)
+    y = codec.decompress_flagged(gs, n, eb, flags, want=9, stream_bytes=s.size)
+    assert codec.status() == 0
+    np.testing.assert_array_equal(y.cpu().numpy(), want)
+
+
+def test_corrupted_rate_bytes_are_contained():
+    n, eb = 50_000, 1e-4
+    x = np.random.default_rng(1).normal(0, 0.01, n).astype(np.float32)
+    s = ops.cpu_compress(x, eb).copy()
+    s[10:200] = 0xFF  # claims 31 planes + 4 outlier bytes per block: far more payload than exists
+    codec = ops.Codec(n)
+    y = codec.decompress(torch.from_numpy(s).cuda(), n, eb)
+    assert codec.status() == 2  # truncated: rate bytes imply more bytes than the stream has
+    assert y.numel() == n
+    out, size = codec.compress(torch.from_numpy(x).cuda(), eb)  # still usable
+    assert codec.status() == 0

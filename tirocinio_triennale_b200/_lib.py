@@ -54,6 +54,8 @@ def _declare_cuda(lib):
     sz, f, i = C.c_size_t, C.c_float, C.c_int
     lib.hc_codec_workspace_bytes.restype = sz
     lib.hc_codec_workspace_bytes.argtypes = [sz]
+    lib.hc_tile_elems.restype = sz
+    lib.hc_tile_elems.argtypes = []
     lib.hc_status_string.restype = C.c_char_p
     lib.hc_status_string.argtypes = [i]
     lib.hc_codec_destroy.restype = None
@@ -65,6 +67,7 @@ def _declare_cuda(lib):
         "hc_codec_status": [vp, i],
         "hc_compress": [vp, vp, sz, f, i, vp, sz, vp, vp],
         "hc_decompress": [vp, vp, sz, sz, f, i, vp, vp],
+        "hc_decompress_flagged": [vp, vp, sz, sz, f, i, vp, vp, C.c_uint, vp],
         "hc_hom_add_f32": [vp, vp, sz, vp, sz, f, i, vp, sz, vp, vp],
         "hc_hom_add_i32": [vp, vp, sz, vp, sz, i, vp, sz, vp, vp],
         "hc_hom_add_stream": [vp, vp, sz, vp, sz, sz, i, vp, sz, vp, vp],

@@ -89,6 +89,22 @@ class Codec:
                                               _stream_ptr()), "decompress")
         return out
 
+    def decompress_flagged(self, stream: torch.Tensor, n: int, eb: float, tile_flags: torch.Tensor, want: int,
+                           mode="outlier", out=None, stream_bytes=None):
+        """Decode tile by tile as ``tile_flags[t] == want`` (uint32/int32, one per ``tile_elems`` values)."""
+        if out is None:
+            out = torch.empty(n, dtype=torch.float32, device=self.device)
+        nbytes = stream.numel() if stream_bytes is None else int(stream_bytes)
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.hc_decompress_flagged(self._h, stream.data_ptr(), nbytes, n, eb, _mode(mode),
+                                                      out.data_ptr(), tile_flags.data_ptr(), int(want),
+                                                      _stream_ptr()), "decompress_flagged")
+        return out
+
+    @property
+    def tile_elems(self) -> int:
+        return int(self.lib.hc_tile_elems())
+
     def hom_add(self, stream: torch.Tensor, local: torch.Tensor, eb: float, mode="outlier", out=None, size=None,
                 stream_bytes=None):
         """stream (+) fp32 -> stream (fused quantise + add in the delta domain + re-encode)."""
