@@ -215,7 +215,8 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
     const int sj = j % NS;
     if (!wait_or_flag(&sh.moved[sj], (j / NS) & 1, ws, abort)) return;
     if ((uint32_t)lane < p.n_dst && p.out_ready[lane] != nullptr) {
-      __threadfence_system();
+      // release at system scope: the compute threads' stores were observed through the mbarrier
+      // above, so they are ordered before this flag for any acquirer (no separate fence needed)
       st_release_sys_u32(p.out_ready[lane] + sh.tile[j & 7], sh.out_ok[sj] ? p.ring_epoch : 0xffffffffu);
     }
     __syncwarp();
