@@ -45,13 +45,15 @@ int encode_call(hc_codec* c, int op, int mode, const void* local, const uint8_t*
   }
   hc::EncParams p;
   memset(&p, 0, sizeof(p));
-  p.local = local;
-  p.n = n;
+  p.n_seg = 1;
+  p.local[0] = local;
+  p.n[0] = n;
   p.recip = 0.5f / eb;
-  p.in = in;
-  p.in_size = in_size;
-  p.in2 = in2;
-  p.in2_size = in2_size;
+  p.n_in = in2 ? 2u : (in ? 1u : 0u);
+  p.in[0] = in;
+  p.in_size[0] = in_size;
+  p.in[1] = in2;
+  p.in_size[1] = in2_size;
   p.n_dst = 1;
   p.out[0] = out;
   p.out_cap = cap;

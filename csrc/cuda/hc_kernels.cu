@@ -156,13 +156,12 @@ __host__ __device__ constexpr int enc_smem_base(int op) { return 1024 + enc_stag
 
 template <int OP, int MODE>
 __global__ void __launch_bounds__(kEncThreads, OP == kOpCompress ? 4 : 3)
-hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
+hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ EncShared sh;
   constexpr bool kHasLocal = OP != kOpAddStream;
   constexpr bool kHasIn = OP != kOpCompress;
-  constexpr int kStreams = OP == kOpAddStream ? 2 : (kHasIn ? 1 : 0);
   constexpr int NS = enc_stages(OP);
   uint8_t* const stage0 = smem + 1024;
   uint8_t* cbuf[2] = {smem + enc_smem_base(OP), smem + enc_smem_base(OP) + kBufBytes};
@@ -171,11 +170,29 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const Workspace& ws = p.ws;
-  const bool tma = kHasLocal && p.use_tma;
-  const uint64_t nrate = rate_bytes(p.n);
-  // rows the tensor map covers: int32 deltas come in whole blocks, fp32 data may end in a ragged row
-  const uint64_t full_rows = OP == kOpAddI32 ? num_blocks(p.n) : p.n / kBlock;
-  const uint64_t n_local = OP == kOpAddI32 ? num_blocks(p.n) * kBlock : p.n;
+  const uint32_t Q = kHasIn ? p.n_in : 0u;  // input streams summed into every tile
+  const uint32_t groups_per_seg = p.tiles_per_seg / 32 + 1;
+
+  // what a role needs to know about the segment a tile belongs to
+  struct Seg {
+    uint32_t g, lt;      // segment, tile inside the segment
+    uint64_t n, nrate;   // values and rate bytes of the segment
+    uint64_t full_rows;  // rows the tensor map covers (int32 deltas come in whole blocks)
+    uint64_t n_local;    // readable 4-byte values of the local operand
+  };
+  auto seg_of = [&](uint32_t tile) -> Seg {
+    Seg v;
+    v.g = p.n_seg > 1 ? tile / p.tiles_per_seg : 0u;
+    v.lt = tile - v.g * p.tiles_per_seg;
+    v.n = p.n[v.g];
+    v.nrate = rate_bytes(v.n);
+    v.full_rows = OP == kOpAddI32 ? num_blocks(v.n) : v.n / kBlock;
+    v.n_local = OP == kOpAddI32 ? num_blocks(v.n) * kBlock : v.n;
+    return v;
+  };
+  // destinations of a tile: every destination of the single segment, or the segment's own one
+  auto dst_first = [&](const Seg& v) -> uint32_t { return p.n_seg > 1 ? v.g : 0u; };
+  auto dst_count = [&](const Seg&) -> uint32_t { return p.n_seg > 1 ? 1u : p.n_dst; };
 
   if (tid == 0) {
     for (int i = 0; i < kMaxStages; ++i) {
@@ -201,70 +218,73 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
   auto move_out = [&](uint32_t j) {  // compute threads: tile number j of this CTA -> global memory
     const int sj = j % NS;
     wait_or_flag(&sh.base_ready[sj], (j / NS) & 1, ws, abort);
-    const uint32_t tile = sh.tile[j & 7];
-    const bool ok = sh.out_ok[sj] != 0;
-    if (ok) copy_out(stage0 + sj * kStagePitch, p.out, p.n_dst, sh.out_base[sj], sh.out_tot[sj], tid, kComputeThreads);
-    (void)tile;
-    mbar_arrive(&sh.moved[sj]);       // the scanner raises the consumers' arrival flags (ring steps)
+    const Seg v = seg_of(sh.tile[j & 7]);
+    if (sh.out_ok[sj])
+      copy_out(stage0 + sj * kStagePitch, p.out + dst_first(v), dst_count(v), sh.out_base[sj], sh.out_tot[sj], tid,
+               kComputeThreads);
+    mbar_arrive(&sh.moved[sj]);       // the scanner raises the consumers' arrival flags (collective steps)
     mbar_arrive(&sh.stage_free[sj]);  // the loader may refill the stage
   };
-  // scanner warp, ring steps only: once the compute threads have stored tile j of this CTA, fence
-  // at system scope and raise the tile's arrival flag on every destination.  Doing this here keeps
-  // the system fence (a round trip to the peers) off the compute warps.
+  // scanner warp, collective steps only: once the compute threads have stored tile j of this CTA,
+  // raise the tile's arrival flag on every destination with a release at system scope (the stores
+  // were observed through the mbarrier, so they are ordered before the flag for any acquirer).
+  // Doing this here keeps the wait for the peers' write acknowledgements off the compute warps.
   auto raise_flags = [&](uint32_t j) {
     const int sj = j % NS;
     if (!wait_or_flag(&sh.moved[sj], (j / NS) & 1, ws, abort)) return;
-    if ((uint32_t)lane < p.n_dst && p.out_ready[lane] != nullptr) {
-      // release at system scope: the compute threads' stores were observed through the mbarrier
-      // above, so they are ordered before this flag for any acquirer (no separate fence needed)
-      st_release_sys_u32(p.out_ready[lane] + sh.tile[j & 7], sh.out_ok[sj] ? p.ring_epoch : 0xffffffffu);
+    const Seg v = seg_of(sh.tile[j & 7]);
+    if ((uint32_t)lane < dst_count(v)) {
+      uint32_t* flags = p.out_ready[dst_first(v) + lane];
+      if (flags) st_release_sys_u32(flags + v.lt, sh.out_ok[sj] ? p.ring_epoch : 0xffffffffu);
     }
     __syncwarp();
   };
 
-  // One input stream: its staging buffer alternates with the tile counter (buffer k & 1, use k >> 1).
-  // Two input streams: stream q owns buffer q (use k).
-  auto in_buf = [&](uint32_t k, int q) -> int { return kStreams == 1 ? (int)(k & 1) : q; };
-  auto in_use = [&](uint32_t k) -> uint32_t { return kStreams == 1 ? (k >> 1) : k; };
-
   if (warp == kComputeThreads / 32) {
     // ================================ loader warp ================================================
-    // Software pipeline over this CTA's tiles: the ticket is taken two turns ahead and the input
-    // stream's rate bytes one turn ahead, so neither round trip sits between two look-backs.  Per
-    // tile: input stream first (its aggregate is published before any wait on this CTA's compute
-    // warps), then the fp32 tile's TMA load once its stage is free.
+    // Software pipeline over this CTA's tiles: the ticket is taken two turns ahead and the rate
+    // bytes of the next input tile one turn ahead, so neither round trip sits between two
+    // look-backs.  Per tile: the input streams first (their aggregates are published before any
+    // wait on this CTA's compute warps), then the fp32 tile's TMA load once its stage is free.
+    // Input stream q of this CTA's k-th tile is staging job v = k * Q + q: buffer v & 1.
     auto take = [&]() -> uint32_t {
       uint32_t t = kNoTile;
       if (lane == 0 && !*abort) t = atomicAdd(ws.ctrl, 1u);
       t = __shfl_sync(0xffffffffu, t, 0);
       return t < p.n_tiles ? t : kNoTile;
     };
-    auto try_fetch = [&](uint32_t t, uint32_t (&r)[kRatesPerLane]) -> bool {  // non-blocking
-      if (!kHasIn || kStreams != 1 || t == kNoTile) return false;
-      if (p.in_ready && !flag_is_up(p.in_ready + t, p.ring_epoch)) return false;
-      loader_fetch_rates(p.in, p.in_size, t, r);
+    auto try_fetch = [&](uint32_t t, uint32_t q, uint32_t (&r)[kRatesPerLane]) -> bool {  // non-blocking
+      if (!kHasIn || t == kNoTile) return false;
+      if (p.in_ready[q] && !flag_is_up(p.in_ready[q] + t, p.ring_epoch)) return false;
+      loader_fetch_rates(p.in[q], p.in_size[q], t, r);
       return true;
     };
     uint32_t tile = take();
     uint32_t tile_n = tile != kNoTile ? take() : kNoTile;
     uint32_t rates[kRatesPerLane] = {}, rates_n[kRatesPerLane] = {};
-    bool have = try_fetch(tile, rates), have_n = false;
+    bool have = try_fetch(tile, 0, rates), have_n = false;
     for (uint32_t k = 0;; ++k) {
       const int s = k % NS, slot = k & 7;
       const uint32_t tile_nn = (tile != kNoTile && tile_n != kNoTile) ? take() : kNoTile;
-      if (tile != kNoTile) have_n = try_fetch(tile_n, rates_n);
       if (kHasIn && tile != kNoTile) {
-        bool usable = true;
-        if (p.in_ready && !have && !flag_wait_warp(p.in_ready + tile, p.ring_epoch, ws)) usable = false;
+        const uint64_t nrate = rate_bytes(p.n[0]);
+        for (uint32_t q = 0; q < Q; ++q) {
+          const uint32_t v = k * Q + q, b = v & 1u, u = v >> 1;
+          // next staging job: the next stream of this tile, or the first stream of the next tile
+          const bool last_q = q + 1 == Q;
+          have_n = try_fetch(last_q ? tile_n : tile, last_q ? 0u : q + 1, rates_n);
+          bool usable = true;
+          if (!have) {
+            if (p.in_ready[q] && !flag_wait_warp(p.in_ready[q] + tile, p.ring_epoch, ws)) usable = false;
+            if (usable) loader_fetch_rates(p.in[q], p.in_size[q], tile, rates);
+          }
+          const Chain chain{ws.st_a + (size_t)q * p.tiles_per_seg, ws.grp_a + (size_t)q * groups_per_seg};
+          loader_stage_stream(p.in[q], p.in_size[q], nrate, tile, chain, ws, cbuf[b], &sh.in_full[b], sh.in_rel[b],
+                              sh.in_rate[b], &sh.in_phase[b], usable, rates, &sh.in_free[b], (u - 1) & 1, u >= 1,
+                              abort);
+          have = have_n;
 #pragma unroll
-        for (int q = 0; q < kStreams; ++q) {
-          const int b = in_buf(k, q);
-          const uint32_t u = in_use(k);
-          if (!(q == 0 && have) && usable) loader_fetch_rates(q ? p.in2 : p.in, q ? p.in2_size : p.in_size, tile, rates);
-          loader_stage_stream(q ? p.in2 : p.in, q ? p.in2_size : p.in_size, nrate, tile,
-                              q ? Chain{ws.st_b, ws.grp_b} : Chain{ws.st_a, ws.grp_a}, ws, cbuf[b], &sh.in_full[b],
-                              sh.in_rel[b], sh.in_rate[b], &sh.in_phase[b], usable, rates, &sh.in_free[b], (u - 1) & 1,
-                              u >= 1, abort);
+          for (int i = 0; i < kRatesPerLane; ++i) rates[i] = rates_n[i];
         }
       }
       // stage s is free once the tile packed there NS turns ago has been moved out
@@ -272,41 +292,43 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
       if (k >= NS && !wait_or_flag(&sh.stage_free[s], ((k / NS) - 1) & 1, ws, abort)) t_stage = kNoTile;
       if (lane == 0) {
         sh.tile[slot] = t_stage;
-        const bool fetch = tma && t_stage != kNoTile && (uint64_t)t_stage * kTileBlocks < full_rows;
-        sh.tile_tma[slot] = fetch ? 1u : 0u;
-        if (fetch) {
-          fence_proxy_async();
-          mbar_expect_tx(&sh.tma_full[s], kTileBytes);
-          tma_load_2d(stage0 + s * kStagePitch, &tmap, 0, (int)(t_stage * kTileBlocks), &sh.tma_full[s]);
-        } else {
-          mbar_arrive(&sh.tma_full[s]);
+        bool fetch = false;
+        if (kHasLocal && t_stage != kNoTile) {
+          const Seg v = seg_of(t_stage);
+          fetch = p.use_tma[v.g] && (uint64_t)v.lt * kTileBlocks < v.full_rows;
+          if (fetch) {
+            fence_proxy_async();
+            mbar_expect_tx(&sh.tma_full[s], kTileBytes);
+            tma_load_2d(stage0 + s * kStagePitch, &tmaps.m[v.g], 0, (int)(v.lt * kTileBlocks), &sh.tma_full[s]);
+          }
         }
+        sh.tile_tma[slot] = fetch ? 1u : 0u;
+        if (!fetch) mbar_arrive(&sh.tma_full[s]);
       }
       if (t_stage == kNoTile) break;
       tile = tile_n;
       tile_n = tile_nn;
-      have = have_n;
-#pragma unroll
-      for (int i = 0; i < kRatesPerLane; ++i) rates[i] = rates_n[i];
     }
   } else if (warp == kComputeThreads / 32 + 1) {
     // ================================ scanner warp ===============================================
     // runs the decoupled look-back of the output stream as soon as a tile's total is known, while
     // the compute warps are still transposing and packing; hands them the tile's global offset
-    const bool ring = p.out_ready[0] != nullptr;
+    const bool collective = p.out_ready[0] != nullptr;
     for (uint32_t k = 0;; ++k) {
       const int s = k % NS;
       const uint32_t par = (k / NS) & 1;
       if (!wait_or_flag(&sh.scan_done[s], par, ws, abort)) break;
       const uint32_t tile = sh.tile[k & 7];
       if (tile == kNoTile) {
-        if (ring && kLag && k >= 1) raise_flags(k - 1);  // the tile that left one turn late
+        if (collective && kLag && k >= 1) raise_flags(k - 1);  // the tile that left one turn late
         break;
       }
+      const Seg v = seg_of(tile);
       const uint32_t tot = sh.out_tot[s];
       bool ok = true;
-      const uint64_t excl = lookback(Chain{ws.st_out, ws.grp_out}, tile, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
-      const uint64_t goff = nrate + excl;
+      const Chain chain{ws.st_out + (size_t)v.g * p.tiles_per_seg, ws.grp_out + (size_t)v.g * groups_per_seg};
+      const uint64_t excl = lookback(chain, v.lt, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
+      const uint64_t goff = v.nrate + excl;
       if (ok && goff + tot > p.out_cap) {
         if (lane == 0) note_error(ws.ctrl, kErrCapacity);
         ok = false;
@@ -315,11 +337,11 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
         sh.out_base[s] = goff;
         sh.out_ok[s] = ok ? 1u : 0u;
         mbar_arrive(&sh.base_ready[s]);
-        if (ok && tile == p.n_tiles - 1 && p.size_out) *p.size_out = goff + tot;
+        if (ok && v.lt == p.tiles_per_seg - 1 && p.size_out) p.size_out[v.g] = goff + tot;
         if (fatal_error(ws.ctrl)) *abort = 1;
       }
       __syncwarp();
-      if (ring && k >= (uint32_t)kLag) raise_flags(k - kLag);
+      if (collective && k >= (uint32_t)kLag) raise_flags(k - kLag);
     }
   } else {
     // ================================ compute warps ==============================================
@@ -336,29 +358,25 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
         if (tid == 0) mbar_arrive(&sh.scan_done[s]);  // wakes the scanner, which sees the end marker too
         break;
       }
+      const Seg v = seg_of(tile);
       int32_t d[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) d[i] = 0;
 
-      // ---- incoming stream(s) -> signed deltas ------------------------------------------------
+      // ---- incoming stream(s) -> signed deltas, summed -------------------------------------------
       if (kHasIn) {
-#pragma unroll
-        for (int q = 0; q < kStreams; ++q) {
-          const int b = in_buf(k, q);
-          const bool staged = wait_or_flag(&sh.in_full[b], in_use(k) & 1, ws, abort);
+        for (uint32_t q = 0; q < Q; ++q) {
+          const uint32_t vv = k * Q + q, b = vv & 1u;
+          const bool staged = wait_or_flag(&sh.in_full[b], (vv >> 1) & 1, ws, abort);
           const uint32_t rate_in = staged ? sh.in_rate[b][tid] : 0u;
           const uint32_t pos = sh.in_phase[b] + sh.in_rel[b][tid];
           int W = plane_width(rate_in & 31u);
           W = __reduce_max_sync(0xffffffffu, W);
           if (__any_sync(0xffffffffu, rate_in != 0)) {
-            if (q == 0) {
-              decode_block(cbuf[b], pos, rate_in, W, d);
-            } else {
-              int32_t d2[32];
-              decode_block(cbuf[b], pos, rate_in, W, d2);
+            int32_t d2[32];
+            decode_block(cbuf[b], pos, rate_in, W, d2);
 #pragma unroll
-              for (int i = 0; i < 32; ++i) d[i] += d2[i];
-            }
+            for (int i = 0; i < 32; ++i) d[i] += d2[i];
           }
           mbar_arrive(&sh.in_free[b]);
         }
@@ -367,8 +385,8 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
       // ---- local operand -------------------------------------------------------------------------
       if (kHasLocal) {
         uint32_t w[32];
-        const uint64_t row = (uint64_t)tile * kTileBlocks + tid;
-        if (tma) {
+        const uint64_t row = (uint64_t)v.lt * kTileBlocks + tid;
+        if (p.use_tma[v.g]) {
           if (sh.tile_tma[slot]) {
             load_row_swizzled(stage_s, tid, w);  // rows past the map were zero-filled by the TMA unit
           } else {
@@ -376,10 +394,10 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
             for (int i = 0; i < 32; ++i) w[i] = 0;
           }
           // the ragged last row of fp32 data is not part of the tensor map
-          if (OP != kOpAddI32 && row * kBlock < p.n && (row + 1) * kBlock > p.n)
-            load_row_global((const uint32_t*)p.local, p.n, row, w);
+          if (OP != kOpAddI32 && row * kBlock < v.n && (row + 1) * kBlock > v.n)
+            load_row_global((const uint32_t*)p.local[v.g], v.n, row, w);
         } else {
-          load_row_global((const uint32_t*)p.local, n_local, row, w);
+          load_row_global((const uint32_t*)p.local[v.g], v.n_local, row, w);
         }
         if (OP == kOpAddI32) {
 #pragma unroll
@@ -404,15 +422,17 @@ hc_encode_kernel(const __grid_constant__ CUtensorMap tmap, const EncParams p) {
       const uint32_t rel = compute_exclusive_scan(code.len, sh.wsum[k & 1], &tot);
       if (tid == 0) {
         // publish the tile aggregate right away: successors can look back through this tile
-        if (tile != 0) st_relaxed_gpu_u64(ws.st_out + tile, st_pack(kStAgg, ws.epoch, tot));
+        if (v.lt != 0)
+          st_relaxed_gpu_u64(ws.st_out + (size_t)v.g * p.tiles_per_seg + v.lt, st_pack(kStAgg, ws.epoch, tot));
         sh.out_tot[s] = tot;
         mbar_arrive(&sh.scan_done[s]);
       }
       // rate bytes (section A) go straight to every destination
       {
-        const uint64_t bidx = (uint64_t)tile * kTileBlocks + tid;
+        const uint64_t bidx = (uint64_t)v.lt * kTileBlocks + tid;
+        const uint32_t d0 = dst_first(v), dn = dst_count(v);
 #pragma unroll 1
-        for (uint32_t dsti = 0; dsti < p.n_dst; ++dsti) p.out[dsti][bidx] = (uint8_t)code.rate;
+        for (uint32_t dsti = 0; dsti < dn; ++dsti) p.out[d0 + dsti][bidx] = (uint8_t)code.rate;
       }
       int W = plane_width(code.rate & 31u);
       W = __reduce_max_sync(0xffffffffu, W);
@@ -686,7 +706,7 @@ cudaError_t set_smem(K kernel, int bytes) {
 }
 
 template <int OP, int MODE>
-cudaError_t launch_encode_t(const CUtensorMap& map, const EncParams& p, int grid, cudaStream_t stream) {
+cudaError_t launch_encode_t(const TensorMaps& map, const EncParams& p, int grid, cudaStream_t stream) {
   constexpr int smem = OP == kOpCompress ? kEncSmemLocalOnly : kEncSmemWithIn;
   static thread_local bool attr_done[64] = {};
   int dev = 0;
@@ -701,7 +721,7 @@ cudaError_t launch_encode_t(const CUtensorMap& map, const EncParams& p, int grid
 }
 
 template <int OP>
-cudaError_t launch_encode_m(int mode, const CUtensorMap& map, const EncParams& p, int grid, cudaStream_t stream) {
+cudaError_t launch_encode_m(int mode, const TensorMaps& map, const EncParams& p, int grid, cudaStream_t stream) {
   switch (mode) {
     case kModeOutlier: return launch_encode_t<OP, kModeOutlier>(map, p, grid, stream);
     case kModePlain: return launch_encode_t<OP, kModePlain>(map, p, grid, stream);
@@ -760,22 +780,30 @@ int grid_for_tiles(uint32_t n_tiles, int ctas_per_sm) {
 }
 
 cudaError_t launch_encode(int op, int mode, EncParams p, cudaStream_t stream) {
-  if (p.n == 0) return cudaSuccess;
-  p.n_tiles = (uint32_t)(rate_bytes(p.n) / kTileBlocks);
-  CUtensorMap map;
-  memset(&map, 0, sizeof(map));
-  p.use_tma = 0;
-  if (op != kOpAddStream) {
-    // int32 deltas are stored in whole blocks; fp32 data may end in a ragged row
-    uint64_t rows = op == kOpAddI32 ? num_blocks(p.n) : p.n / kBlock;
-    p.use_tma = make_rows_map(&map, p.local, rows) ? 1u : 0u;
+  if (p.n_seg == 0 || p.n_seg > (uint32_t)kMaxDst || p.n_in > (uint32_t)kMaxIn) return cudaErrorInvalidValue;
+  if (p.n_seg > 1 && (op != kOpCompress || p.n_in != 0)) return cudaErrorInvalidValue;
+  if (op == kOpCompress) p.n_in = 0;
+  uint64_t n_max = 0;
+  for (uint32_t g = 0; g < p.n_seg; ++g) n_max = p.n[g] > n_max ? p.n[g] : n_max;
+  if (n_max == 0) return cudaSuccess;
+  p.tiles_per_seg = (uint32_t)(rate_bytes(n_max) / kTileBlocks);
+  p.n_tiles = p.tiles_per_seg * p.n_seg;
+  TensorMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  for (uint32_t g = 0; g < p.n_seg; ++g) {
+    p.use_tma[g] = 0;
+    if (op != kOpAddStream && p.n[g]) {
+      // int32 deltas are stored in whole blocks; fp32 data may end in a ragged row
+      uint64_t rows = op == kOpAddI32 ? num_blocks(p.n[g]) : p.n[g] / kBlock;
+      p.use_tma[g] = make_rows_map(&maps.m[g], p.local[g], rows) ? 1u : 0u;
+    }
   }
   int grid = grid_for_tiles(p.n_tiles, op == kOpCompress ? 4 : 3);
   switch (op) {
-    case kOpCompress: return launch_encode_m<kOpCompress>(mode, map, p, grid, stream);
-    case kOpAddF32: return launch_encode_m<kOpAddF32>(mode, map, p, grid, stream);
-    case kOpAddI32: return launch_encode_m<kOpAddI32>(mode, map, p, grid, stream);
-    case kOpAddStream: return launch_encode_m<kOpAddStream>(mode, map, p, grid, stream);
+    case kOpCompress: return launch_encode_m<kOpCompress>(mode, maps, p, grid, stream);
+    case kOpAddF32: return launch_encode_m<kOpAddF32>(mode, maps, p, grid, stream);
+    case kOpAddI32: return launch_encode_m<kOpAddI32>(mode, maps, p, grid, stream);
+    case kOpAddStream: return launch_encode_m<kOpAddStream>(mode, maps, p, grid, stream);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -56,23 +56,31 @@ struct Workspace {
   uint64_t spin_limit_ns;
 };
 
+// A launch of the stream-producing kernel.
+//   * up to kMaxDst input streams are summed into every tile (n_in; 0 for compress);
+//   * the output goes either to n_dst destinations that all receive the same stream (n_seg == 1:
+//     a ring step, or the reduced chunk pushed to every rank), or, for compress only, to n_seg
+//     independent streams ("segments": segment g compresses local[g] of n[g] values into out[g]);
+//     segments own tiles_per_seg consecutive tickets and their own look-back chain.
+constexpr int kMaxIn = kMaxDst;
 struct EncParams {
-  const void* local;  // fp32 values or int32 deltas of this call
-  uint64_t n;
-  uint32_t n_tiles;
-  uint32_t use_tma;
-  float recip;  // 0.5f / eb
-  const uint8_t* in;
-  uint64_t in_size;
-  const uint8_t* in2;
-  uint64_t in2_size;
-  const uint32_t* in_ready;  // one arrival flag per tile (ring steps), or null
+  const void* local[kMaxDst];  // fp32 values or int32 deltas, per segment
+  uint64_t n[kMaxDst];         // values per segment
+  uint32_t use_tma[kMaxDst];
+  uint32_t n_seg;
+  uint32_t tiles_per_seg;
+  uint32_t n_tiles;  // n_seg * tiles_per_seg
+  uint32_t n_in;
+  float recip;       // 0.5f / eb
+  const uint8_t* in[kMaxIn];
+  uint64_t in_size[kMaxIn];
+  const uint32_t* in_ready[kMaxIn];  // one arrival flag per tile, or null
   uint32_t ring_epoch;
-  uint32_t n_dst;
-  uint8_t* out[kMaxDst];
-  uint32_t* out_ready[kMaxDst];  // arrival flags on the consumers, or null entries
+  uint32_t n_dst;                // destinations of the single segment (ignored when n_seg > 1)
+  uint8_t* out[kMaxDst];         // n_seg == 1: destinations; n_seg > 1: out[g] of segment g
+  uint32_t* out_ready[kMaxDst];  // arrival flags on the consumers, laid out like `out`, or null
   uint64_t out_cap;
-  uint64_t* size_out;  // device word receiving the exact stream length (may be null)
+  uint64_t* size_out;  // device words receiving the exact stream length of each segment (or null)
   Workspace ws;
 };
 

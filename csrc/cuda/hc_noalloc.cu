@@ -59,8 +59,9 @@ int hc_compress_noalloc(const float* d_x, size_t n, float eb, uint8_t* d_out, si
   }
   hc::EncParams p;
   memset(&p, 0, sizeof(p));
-  p.local = d_x;
-  p.n = n;
+  p.n_seg = 1;
+  p.local[0] = d_x;
+  p.n[0] = n;
   p.recip = 0.5f / eb;
   p.n_dst = 1;
   p.out[0] = d_out;

@@ -209,17 +209,19 @@ int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, f
     if (n == 0) continue;
     hc::EncParams p;
     memset(&p, 0, sizeof(p));
-    p.local = d_sbuf + (size_t)ch * B;
-    p.n = n;
+    p.n_seg = 1;
+    p.local[0] = d_sbuf + (size_t)ch * B;
+    p.n[0] = n;
     p.recip = 0.5f / eb;
     p.ring_epoch = call;
     p.out_cap = L.slot_bytes;
     p.size_out = c->sizes + s;
     if (s > 0) {
       const size_t slot = L.rs_slot(s);
-      p.in = self + L.data_off(slot);
-      p.in_size = L.slot_bytes;
-      p.in_ready = reinterpret_cast<const uint32_t*>(self + L.flag_off(slot));
+      p.n_in = 1;
+      p.in[0] = self + L.data_off(slot);
+      p.in_size[0] = L.slot_bytes;
+      p.in_ready[0] = reinterpret_cast<const uint32_t*>(self + L.flag_off(slot));
     }
     if (s < P - 1) {
       const size_t slot = L.rs_slot(s + 1);
