@@ -71,6 +71,7 @@ struct hc_comm {
   uint32_t ws_epoch = 0;
   uint32_t call = 0;
   uint32_t raw_call = 0;
+  int algorithm = 1;              // 0 ring (P + 1 kernels), 1 direct (3 kernels)
   bool trace = false;             // record one CUDA event per step of hc_allreduce
   cudaEvent_t ev[hc::kMaxDst + 3] = {};
   int n_ev = 0;
@@ -178,9 +179,7 @@ int hc_comm_last_stream_bytes(hc_comm* c, uint64_t* bytes, int n) {
                                                                                                   : hc::kErrCuda;
 }
 
-int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, float eb, hc_stream_t stream) {
-  if (!c || !d_sbuf || !d_rbuf || !(eb > 0.0f) || count > c->max_count) return hc::kErrArgument;
-  if (count == 0) return hc::kOk;
+static int allreduce_ring(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, float eb, hc_stream_t stream) {
   const int P = c->world, r = c->rank;
   const Layout& L = c->lay;
   const size_t B = hc_chunk_elems(count, P);
@@ -267,6 +266,133 @@ int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, f
   mark();
   return hc::kOk;
 }
+
+}  // extern "C" (collective entry points continue below)
+
+// Direct ("one-shot") form of the same reduction for a switched fabric, three kernels per call:
+//   1. one multi-segment compress: chunk d of the local data is compressed straight into rank d's
+//      receive slot for this source, for every d != rank (P-1 segments, peer stores, one arrival
+//      flag per tile);
+//   2. one homomorphic add over the own chunk: the P-1 incoming streams are decoded to deltas,
+//      summed with the quantised local chunk in the integer domain and encoded once; the reduced
+//      stream goes to the all-gather buffer of every rank;
+//   3. the multi-segment decode.
+// Integer addition is associative, so the reduced streams are byte-identical to the ring's (and to
+// hc_cpu_ring_allreduce); only the number of launches and the traffic pattern differ: every rank
+// talks to every other rank at once, which is what NVSwitch is built for.
+static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, float eb, hc_stream_t stream) {
+  const int P = c->world, r = c->rank;
+  const Layout& L = c->lay;
+  const size_t B = hc_chunk_elems(count, P);
+  auto chunk_len = [&](int ch) -> size_t {
+    size_t lo = (size_t)ch * B;
+    if (lo >= count) return 0;
+    size_t hi = lo + B;
+    return (hi > count ? count : hi) - lo;
+  };
+  c->call += 1;
+  if (c->call == 0) c->call = 1;
+  const uint32_t call = c->call;
+  const int parity = (int)(call & 1u);
+  uint8_t* self = c->peer[r];
+  c->n_ev = 0;
+  auto mark = [&]() {
+    if (c->trace) cudaEventRecord(c->ev[c->n_ev++], stream);
+  };
+  mark();
+  // ---- 1. scatter: chunk d -> rank d's slot for source r ------------------------------------------
+  if (P > 1) {
+    hc::EncParams p;
+    memset(&p, 0, sizeof(p));
+    p.recip = 0.5f / eb;
+    p.ring_epoch = call;
+    p.out_cap = L.slot_bytes;
+    p.size_out = c->sizes;
+    for (int k = 1; k < P; ++k) {
+      const int d = (r + k) % P;
+      const size_t n = chunk_len(d);
+      if (n == 0) continue;
+      const size_t slot = L.rs_slot((r - d + P) % P);  // slots are indexed by distance to the source
+      const uint32_t g = p.n_seg++;
+      p.local[g] = d_sbuf + (size_t)d * B;
+      p.n[g] = n;
+      p.out[g] = c->peer[d] + L.data_off(slot);
+      p.out_ready[g] = reinterpret_cast<uint32_t*>(c->peer[d] + L.flag_off(slot));
+    }
+    if (p.n_seg) {
+      p.n_dst = 1;
+      p.ws = next_ws(c, stream);
+      if (hc::launch_encode(hc::kOpCompress, hc::kModeOutlier, p, stream) != cudaSuccess) return hc::kErrCuda;
+    }
+  }
+  mark();
+  // ---- 2. reduce the own chunk and push the result to everybody -----------------------------------
+  if (const size_t n = chunk_len(r)) {
+    hc::EncParams p;
+    memset(&p, 0, sizeof(p));
+    p.n_seg = 1;
+    p.local[0] = d_sbuf + (size_t)r * B;
+    p.n[0] = n;
+    p.recip = 0.5f / eb;
+    p.ring_epoch = call;
+    p.out_cap = L.slot_bytes;
+    p.size_out = c->sizes + (P - 1);  // after the P-1 scattered streams
+    for (int k = 1; k < P; ++k) {
+      const size_t slot = L.rs_slot(k);
+      const uint32_t q = p.n_in++;
+      p.in[q] = self + L.data_off(slot);
+      p.in_size[q] = L.slot_bytes;
+      p.in_ready[q] = reinterpret_cast<const uint32_t*>(self + L.flag_off(slot));
+    }
+    const size_t slot = L.ag_slot(parity, r);
+    p.n_dst = (uint32_t)P;
+    for (int k = 0; k < P; ++k) {
+      const int dst = (r + k) % P;
+      p.out[k] = c->peer[dst] + L.data_off(slot);
+      p.out_ready[k] = reinterpret_cast<uint32_t*>(c->peer[dst] + L.flag_off(slot));
+    }
+    p.ws = next_ws(c, stream);
+    if (hc::launch_encode(P > 1 ? hc::kOpAddF32 : hc::kOpCompress, hc::kModeOutlier, p, stream) != cudaSuccess)
+      return hc::kErrCuda;
+  }
+  mark();
+  // ---- 3. decode the P reduced chunks as their tiles arrive ----------------------------------------
+  hc::DecParams d;
+  memset(&d, 0, sizeof(d));
+  d.eb = eb;
+  d.ring_epoch = call;
+  for (int k = 0; k < P; ++k) {
+    const int ch = (r + k) % P;  // own chunk first: it is produced locally
+    const size_t n = chunk_len(ch);
+    if (n == 0) continue;
+    const size_t slot = L.ag_slot(parity, ch);
+    hc::DecSegment& sg = d.seg[d.n_seg++];
+    sg.in = self + L.data_off(slot);
+    sg.in_size = L.slot_bytes;
+    sg.in_ready = reinterpret_cast<const uint32_t*>(self + L.flag_off(slot));
+    sg.out = d_rbuf + (size_t)ch * B;
+    sg.n = n;
+  }
+  d.ws = next_ws(c, stream);
+  if (hc::launch_decode(hc::kModeOutlier, d, stream) != cudaSuccess) return hc::kErrCuda;
+  mark();
+  return hc::kOk;
+}
+
+extern "C" int hc_comm_set_algorithm(hc_comm* c, int algorithm) {
+  if (!c || algorithm < 0 || algorithm > 1) return hc::kErrArgument;
+  c->algorithm = algorithm;
+  return hc::kOk;
+}
+
+extern "C" int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, float eb, hc_stream_t stream) {
+  if (!c || !d_sbuf || !d_rbuf || !(eb > 0.0f) || count > c->max_count) return hc::kErrArgument;
+  if (count == 0) return hc::kOk;
+  return c->algorithm == 0 ? allreduce_ring(c, d_sbuf, d_rbuf, count, eb, stream)
+                           : allreduce_direct(c, d_sbuf, d_rbuf, count, eb, stream);
+}
+
+extern "C" {
 
 // ---- uncompressed allreduce over the same peer mappings ------------------------------------------
 // Two-shot direct algorithm for NVSwitch: every rank stages its input in its symmetric region,

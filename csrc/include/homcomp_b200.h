@@ -108,6 +108,10 @@ int hc_comm_status(hc_comm* c, int clear);  // synchronises; sticky hc::Status
 // Sum of `count` floats over all ranks, error at most world * eb per value; d_sbuf and d_rbuf may
 // alias.  Enqueues world + 1 kernels on `stream`; never allocates or synchronises.
 int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, float eb, hc_stream_t stream);
+// algorithm 0: ring reduce-scatter with one fused kernel per hop (world + 1 launches);
+// algorithm 1 (default): direct scatter -> reduce -> gather for a switched fabric (3 launches).
+// Both produce byte-identical reduced streams, hence bit-identical results.
+int hc_comm_set_algorithm(hc_comm* c, int algorithm);
 // Uncompressed sum over the same peer mappings (two-shot direct algorithm, three kernels); the
 // compressed and the uncompressed collective of one handle must not be in flight together.
 int hc_allreduce_raw(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, hc_stream_t stream);

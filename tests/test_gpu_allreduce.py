@@ -8,14 +8,14 @@ from mp_util import run_ranks
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 
-def _worker(rank, world, counts, eb):
+def _worker(rank, world, counts, eb, algorithm="direct"):
     import torch.distributed as dist
 
     from datasets import gradient_like, smooth
     from tirocinio_triennale_b200 import ops
     from tirocinio_triennale_b200.parallel import CompressedAllreduce
 
-    ar = CompressedAllreduce(max(counts), timeout_ms=5000)
+    ar = CompressedAllreduce(max(counts), timeout_ms=5000, algorithm=algorithm)
     for it, n in enumerate(counts):
         gen = smooth if it % 2 == 0 else gradient_like
         bufs = [gen(n, seed=100 * it + r) for r in range(world)]
@@ -38,12 +38,13 @@ def _worker(rank, world, counts, eb):
     ar.close()
 
 
+@pytest.mark.parametrize("algorithm", ["direct", "ring"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_allreduce_matches_host_oracle(world):
+def test_allreduce_matches_host_oracle(world, algorithm):
     if torch.cuda.device_count() < world:
         pytest.skip("needs %d GPUs" % world)
     counts = [1, 33, 4097, 100000, 1 << 20, (1 << 22) + 12345]
-    run_ranks(_worker, world, args=(counts, 1e-4))
+    run_ranks(_worker, world, args=(counts, 1e-4, algorithm))
 
 
 def _raw_worker(rank, world):

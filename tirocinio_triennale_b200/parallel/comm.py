@@ -22,7 +22,8 @@ class CompressedAllreduce:
     ranks and equals ``2 * eb * sum_r quantise(x_r)``: the error is at most ``world * eb``.
     """
 
-    def __init__(self, max_count: int, group=None, device=None, timeout_ms: int | None = None):
+    def __init__(self, max_count: int, group=None, device=None, timeout_ms: int | None = None,
+                 algorithm: str = "direct"):
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed must be initialised (it carries the IPC handles)")
         self.group = group
@@ -56,6 +57,7 @@ class CompressedAllreduce:
             _lib.check(self.lib.hc_comm_create(C.byref(h), self.rank, self.world, self.max_count, ptrs, None),
                        "comm_create")
             self._h = h
+            self.set_algorithm(algorithm)
             if timeout_ms:
                 _lib.check(self.lib.hc_comm_set_timeout_ms(self._h, int(timeout_ms)), "set_timeout")
             torch.cuda.synchronize()
@@ -88,6 +90,13 @@ class CompressedAllreduce:
     def status(self, clear: bool = True) -> int:
         with torch.cuda.device(self.device):
             return int(self.lib.hc_comm_status(self._h, 1 if clear else 0))
+
+    def set_algorithm(self, algorithm: str):
+        """``"ring"``: one fused kernel per reduce-scatter hop (world + 1 launches, the reference's
+        algorithm); ``"direct"``: scatter, reduce, gather in three launches (default).  Same bits."""
+        code = {"ring": 0, "direct": 1}[algorithm]
+        _lib.check(self.lib.hc_comm_set_algorithm(self._h, code), "set_algorithm")
+        self.algorithm = algorithm
 
     def set_trace(self, on: bool = True):
         """Record one CUDA event per step of every following allreduce (see ``last_step_ms``)."""
