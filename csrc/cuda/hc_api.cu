@@ -175,6 +175,57 @@ int hc_decompress_flagged(hc_codec* c, const uint8_t* d_in, size_t in_size, size
 
 size_t hc_tile_elems(void) { return hc::kTileElems; }
 
+// Several independent tensors compressed by one launch (segments); sizes land in d_sizes[g].
+int hc_compress_batch(hc_codec* c, int n_seg, const float* const* d_x, const size_t* n, float eb, int mode,
+                      uint8_t* const* d_out, size_t cap_each, uint64_t* d_sizes, hc_stream_t stream) {
+  if (!c || n_seg < 1 || n_seg > hc::kMaxDst || !(eb > 0.0f) || !d_x || !n || !d_out) return hc::kErrArgument;
+  hc::EncParams p;
+  memset(&p, 0, sizeof(p));
+  size_t total = 0;
+  for (int g = 0; g < n_seg; ++g) {
+    p.local[g] = d_x[g];
+    p.n[g] = n[g];
+    p.out[g] = d_out[g];
+    // whole chunks per segment: that is what the look-back chains of the workspace are sized in
+    total += hc::rate_bytes(n[g]) * hc::kBlock;
+  }
+  if (total > hc::rate_bytes(c->max_elems) * hc::kBlock) return hc::kErrArgument;
+  p.n_seg = (uint32_t)n_seg;
+  p.n_dst = 1;
+  p.recip = 0.5f / eb;
+  p.out_cap = cap_each;
+  p.size_out = d_sizes;
+  p.ws = next_workspace(c, stream);
+  return hc::launch_encode(hc::kOpCompress, mode, p, stream) == cudaSuccess ? hc::kOk : hc::kErrCuda;
+}
+
+// n_in streams (+) fp32 -> stream: every stream is decoded to deltas and summed in the integer
+// domain together with the quantised local values, then encoded once.
+int hc_hom_add_multi(hc_codec* c, int n_in, const uint8_t* const* d_in, const size_t* in_size, const float* d_local,
+                     size_t n, float eb, int mode, uint8_t* d_out, size_t cap, uint64_t* d_size, hc_stream_t stream) {
+  if (int rc = check_call(c, n, eb, true)) return rc;
+  if (n_in < 1 || n_in > hc::kMaxIn || !d_in || !in_size || !d_local || !d_out) return hc::kErrArgument;
+  if ((size_t)n_in * hc::rate_bytes(n) > hc::rate_bytes(c->max_elems) + 64) return hc::kErrArgument;
+  if (n == 0) return hc::kOk;
+  hc::EncParams p;
+  memset(&p, 0, sizeof(p));
+  p.n_seg = 1;
+  p.local[0] = d_local;
+  p.n[0] = n;
+  p.recip = 0.5f / eb;
+  p.n_in = (uint32_t)n_in;
+  for (int q = 0; q < n_in; ++q) {
+    p.in[q] = d_in[q];
+    p.in_size[q] = in_size[q];
+  }
+  p.n_dst = 1;
+  p.out[0] = d_out;
+  p.out_cap = cap;
+  p.size_out = d_size;
+  p.ws = next_workspace(c, stream);
+  return hc::launch_encode(hc::kOpAddF32, mode, p, stream) == cudaSuccess ? hc::kOk : hc::kErrCuda;
+}
+
 int hc_quant_pred(const float* d_x, size_t n, float eb, int mode, int32_t* d_deltas, hc_stream_t stream) {
   if (!(eb > 0.0f) || !d_x || !d_deltas) return hc::kErrArgument;
   return hc::launch_quant_pred(mode, d_x, d_deltas, n, eb, stream) == cudaSuccess ? hc::kOk : hc::kErrCuda;

@@ -266,27 +266,30 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
     for (uint32_t k = 0;; ++k) {
       const int s = k % NS, slot = k & 7;
       const uint32_t tile_nn = (tile != kNoTile && tile_n != kNoTile) ? take() : kNoTile;
-      if (kHasIn && tile != kNoTile) {
+      // staging job q of this tile (input stream q -> buffer (k * Q + q) & 1)
+      auto stage_job = [&](uint32_t q) {
         const uint64_t nrate = rate_bytes(p.n[0]);
-        for (uint32_t q = 0; q < Q; ++q) {
-          const uint32_t v = k * Q + q, b = v & 1u, u = v >> 1;
-          // next staging job: the next stream of this tile, or the first stream of the next tile
-          const bool last_q = q + 1 == Q;
-          have_n = try_fetch(last_q ? tile_n : tile, last_q ? 0u : q + 1, rates_n);
-          bool usable = true;
-          if (!have) {
-            if (p.in_ready[q] && !flag_wait_warp(p.in_ready[q] + tile, p.ring_epoch, ws)) usable = false;
-            if (usable) loader_fetch_rates(p.in[q], p.in_size[q], tile, rates);
-          }
-          const Chain chain{ws.st_a + (size_t)q * p.tiles_per_seg, ws.grp_a + (size_t)q * groups_per_seg};
-          loader_stage_stream(p.in[q], p.in_size[q], nrate, tile, chain, ws, cbuf[b], &sh.in_full[b], sh.in_rel[b],
-                              sh.in_rate[b], &sh.in_phase[b], usable, rates, &sh.in_free[b], (u - 1) & 1, u >= 1,
-                              abort);
-          have = have_n;
-#pragma unroll
-          for (int i = 0; i < kRatesPerLane; ++i) rates[i] = rates_n[i];
+        const uint32_t v = k * Q + q, b = v & 1u, u = v >> 1;
+        // next staging job: the next stream of this tile, or the first stream of the next tile
+        const bool last_q = q + 1 == Q;
+        have_n = try_fetch(last_q ? tile_n : tile, last_q ? 0u : q + 1, rates_n);
+        bool usable = true;
+        if (!have) {
+          if (p.in_ready[q] && !flag_wait_warp(p.in_ready[q] + tile, p.ring_epoch, ws)) usable = false;
+          if (usable) loader_fetch_rates(p.in[q], p.in_size[q], tile, rates);
         }
-      }
+        const Chain chain{ws.st_a + (size_t)q * p.tiles_per_seg, ws.grp_a + (size_t)q * groups_per_seg};
+        loader_stage_stream(p.in[q], p.in_size[q], nrate, tile, chain, ws, cbuf[b], &sh.in_full[b], sh.in_rel[b],
+                            sh.in_rate[b], &sh.in_phase[b], usable, rates, &sh.in_free[b], (u - 1) & 1, u >= 1, abort);
+        have = have_n;
+#pragma unroll
+        for (int i = 0; i < kRatesPerLane; ++i) rates[i] = rates_n[i];
+      };
+      // The first two streams go in before the tile is handed to the compute warps: their buffers
+      // only depend on earlier tiles.  Later streams reuse a buffer that the compute warps free
+      // while working on THIS tile, so they must come after the hand-over.
+      if (kHasIn && tile != kNoTile)
+        for (uint32_t q = 0; q < Q && q < 2; ++q) stage_job(q);
       // stage s is free once the tile packed there NS turns ago has been moved out
       uint32_t t_stage = tile;
       if (k >= NS && !wait_or_flag(&sh.stage_free[s], ((k / NS) - 1) & 1, ws, abort)) t_stage = kNoTile;
@@ -306,6 +309,8 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
         if (!fetch) mbar_arrive(&sh.tma_full[s]);
       }
       if (t_stage == kNoTile) break;
+      if (kHasIn)
+        for (uint32_t q = 2; q < Q; ++q) stage_job(q);
       tile = tile_n;
       tile_n = tile_nn;
     }
@@ -427,8 +432,9 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
         sh.out_tot[s] = tot;
         mbar_arrive(&sh.scan_done[s]);
       }
-      // rate bytes (section A) go straight to every destination
-      {
+      // rate bytes (section A) go straight to every destination; a segment shorter than the longest
+      // one of the launch has tickets past its own section A, which must not touch its payload
+      if ((uint64_t)v.lt * kTileBlocks < v.nrate) {
         const uint64_t bidx = (uint64_t)v.lt * kTileBlocks + tid;
         const uint32_t d0 = dst_first(v), dn = dst_count(v);
 #pragma unroll 1

@@ -85,6 +85,15 @@ int hc_hom_add_i32(hc_codec* c, const uint8_t* d_in, size_t in_size, const int32
                    uint8_t* d_out, size_t cap, uint64_t* d_size, hc_stream_t stream);
 int hc_hom_add_stream(hc_codec* c, const uint8_t* d_a, size_t a_size, const uint8_t* d_b, size_t b_size, size_t n,
                       int mode, uint8_t* d_out, size_t cap, uint64_t* d_size, hc_stream_t stream);
+// Up to 8 independent tensors compressed by one launch; out[g] needs cap_each bytes, d_sizes[g]
+// receives the stream length.  The tensors together (each rounded up to whole 32768-value chunks)
+// must fit the handle's max_elems.
+int hc_compress_batch(hc_codec* c, int n_seg, const float* const* d_x, const size_t* n, float eb, int mode,
+                      uint8_t* const* d_out, size_t cap_each, uint64_t* d_sizes, hc_stream_t stream);
+// Sum of up to 8 streams and one fp32 operand in the quantised domain, encoded once.  n_in * n must
+// fit the handle's max_elems.
+int hc_hom_add_multi(hc_codec* c, int n_in, const uint8_t* const* d_in, const size_t* in_size, const float* d_local,
+                     size_t n, float eb, int mode, uint8_t* d_out, size_t cap, uint64_t* d_size, hc_stream_t stream);
 int hc_quant_pred(const float* d_x, size_t n, float eb, int mode, int32_t* d_deltas, hc_stream_t stream);
 // dst = a + b (+ c) (+ d); c and d may be null; dst may alias a
 int hc_sum(float* d_dst, const float* d_a, const float* d_b, const float* d_c, const float* d_d, size_t n,

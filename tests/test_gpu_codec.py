@@ -143,3 +143,31 @@ def test_sum_kernel(codec):
     torch.testing.assert_close(dst, a + b, rtol=0, atol=0)
     codec.sum(dst, a, b, c, d)
     torch.testing.assert_close(dst, ((a + b) + c) + d, rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("lens", [[1000, 1000], [70000, 33, 8193], [32768 * 3, 5, 32768 * 3 - 1, 100, 200000, 1, 4096, 8192]])
+def test_batched_compress_matches_oracle(lens):
+    eb = 1e-4
+    codec = ops.Codec(max_elems=1 << 22)
+    xs = [ALL["gradient" if i % 2 else "smooth"](n, seed=i) for i, n in enumerate(lens)]
+    outs, sizes = codec.compress_batch([_gpu(x) for x in xs], eb)
+    assert codec.status() == 0
+    for x, o, sz in zip(xs, outs, sizes.tolist()):
+        np.testing.assert_array_equal(o[:sz].cpu().numpy(), ops.cpu_compress(x, eb))
+
+
+@pytest.mark.parametrize("k", [1, 3, 7])
+@pytest.mark.parametrize("n", [33, 8193, 300000])
+def test_multi_stream_add_matches_oracle(k, n):
+    eb = 1e-4
+    codec = ops.Codec(max_elems=1 << 22)
+    xs = [ALL["gradient"](n, seed=10 + i) for i in range(k)]
+    y = ALL["smooth"](n, seed=99)
+    streams = [ops.cpu_compress(x, eb) for x in xs]
+    want = ops.cpu_compress(y, eb)
+    for s in streams:  # the oracle adds stream by stream; integer sums do not care about the order
+        want = ops.cpu_hom_add_streams(want, s, n)
+    gs = [_gpu(np.concatenate([s, np.zeros(32, np.uint8)])) for s in streams]
+    out, size = codec.hom_add_multi(gs, _gpu(y), eb, stream_bytes=[s.size for s in streams])
+    assert codec.status() == 0
+    np.testing.assert_array_equal(_stream(out, size), want)

@@ -72,6 +72,8 @@ def _declare_cuda(lib):
         "hc_hom_add_i32": [vp, vp, sz, vp, sz, i, vp, sz, vp, vp],
         "hc_hom_add_stream": [vp, vp, sz, vp, sz, sz, i, vp, sz, vp, vp],
         "hc_quant_pred": [vp, sz, f, i, vp, vp],
+        "hc_compress_batch": [vp, i, vp, vp, f, i, vp, sz, vp, vp],
+        "hc_hom_add_multi": [vp, i, vp, vp, vp, sz, f, i, vp, sz, vp, vp],
         "hc_sum": [vp, vp, vp, vp, vp, sz, vp],
     }
     for name, args in sigs.items():

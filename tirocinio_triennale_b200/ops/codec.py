@@ -118,6 +118,40 @@ class Codec:
                                                _stream_ptr()), "hom_add")
         return out, size
 
+    def compress_batch(self, xs, eb: float, mode="outlier"):
+        """Compress up to 8 tensors with one launch; returns (list of stream buffers, int64 sizes tensor)."""
+        import ctypes as C
+
+        k = len(xs)
+        for x in xs:
+            self._check_f32(x)
+        cap = max(max_compressed_bytes(x.numel()) for x in xs) + 16
+        outs = [torch.empty(cap, dtype=torch.uint8, device=self.device) for _ in xs]
+        sizes = torch.zeros(k, dtype=torch.int64, device=self.device)
+        xp = (C.c_void_p * k)(*[x.data_ptr() for x in xs])
+        ns = (C.c_size_t * k)(*[x.numel() for x in xs])
+        op = (C.c_void_p * k)(*[o.data_ptr() for o in outs])
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.hc_compress_batch(self._h, k, xp, ns, eb, _mode(mode), op, cap, sizes.data_ptr(),
+                                                  _stream_ptr()), "compress_batch")
+        return outs, sizes
+
+    def hom_add_multi(self, streams, local: torch.Tensor, eb: float, mode="outlier", stream_bytes=None):
+        """streams[0] (+) ... (+) streams[k-1] (+) fp32 -> stream, all summed in the delta domain."""
+        import ctypes as C
+
+        self._check_f32(local)
+        k, n = len(streams), local.numel()
+        out, size = self._out(n, None, None)
+        sp = (C.c_void_p * k)(*[s.data_ptr() for s in streams])
+        nb = (C.c_size_t * k)(*[(s.numel() if stream_bytes is None else int(stream_bytes[i]))
+                                for i, s in enumerate(streams)])
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.hc_hom_add_multi(self._h, k, sp, nb, local.data_ptr(), n, eb, _mode(mode),
+                                                 out.data_ptr(), out.numel(), size.data_ptr(), _stream_ptr()),
+                       "hom_add_multi")
+        return out, size
+
     def quant_pred(self, x: torch.Tensor, eb: float, mode="outlier", out=None):
         self._check_f32(x)
         n = x.numel()
