@@ -26,6 +26,7 @@ struct __align__(16) EncShared {
   uint32_t in_phase[2];             // 16-byte phase of the staged bytes in buffer b
   uint32_t out_tot[kMaxStages];     // payload bytes of the tile in stage s
   uint32_t out_ok[kMaxStages];
+  uint32_t ok_ring[8];              // out_ok by ticket ring slot (flags may be raised several tiles late)
   uint64_t out_base[kMaxStages];    // global byte offset of the tile's payload
   uint32_t wsum[2][kComputeThreads / 32];
   uint32_t abort;
@@ -222,24 +223,9 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
     if (sh.out_ok[sj])
       copy_out(stage0 + sj * kStagePitch, p.out + dst_first(v), dst_count(v), sh.out_base[sj], sh.out_tot[sj], tid,
                kComputeThreads);
-    mbar_arrive(&sh.moved[sj]);       // the scanner raises the consumers' arrival flags (collective steps)
+    mbar_arrive(&sh.moved[sj]);       // the loader raises the consumers' arrival flags (collective steps)
     mbar_arrive(&sh.stage_free[sj]);  // the loader may refill the stage
   };
-  // scanner warp, collective steps only: once the compute threads have stored tile j of this CTA,
-  // raise the tile's arrival flag on every destination with a release at system scope (the stores
-  // were observed through the mbarrier, so they are ordered before the flag for any acquirer).
-  // Doing this here keeps the wait for the peers' write acknowledgements off the compute warps.
-  auto raise_flags = [&](uint32_t j) {
-    const int sj = j % NS;
-    if (!wait_or_flag(&sh.moved[sj], (j / NS) & 1, ws, abort)) return;
-    const Seg v = seg_of(sh.tile[j & 7]);
-    if ((uint32_t)lane < dst_count(v)) {
-      uint32_t* flags = p.out_ready[dst_first(v) + lane];
-      if (flags) st_release_sys_u32(flags + v.lt, sh.out_ok[sj] ? p.ring_epoch : 0xffffffffu);
-    }
-    __syncwarp();
-  };
-
   if (warp == kComputeThreads / 32) {
     // ================================ loader warp ================================================
     // Software pipeline over this CTA's tiles: the ticket is taken two turns ahead and the rate
@@ -259,6 +245,8 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       loader_fetch_rates(p.in[q], p.in_size[q], t, r);
       return true;
     };
+    const bool loader_flags = p.out_ready[0] != nullptr;  // this launch is a step of a collective
+    uint32_t flagged = 0;  // tiles [0, flagged) of this CTA have had their arrival flags raised
     uint32_t tile = take();
     uint32_t tile_n = tile != kNoTile ? take() : kNoTile;
     uint32_t rates[kRatesPerLane] = {}, rates_n[kRatesPerLane] = {};
@@ -308,6 +296,27 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
         sh.tile_tma[slot] = fetch ? 1u : 0u;
         if (!fetch) mbar_arrive(&sh.tma_full[s]);
       }
+      // compress as a collective step: every tile up to k - NS has left its stage (stage_free was
+      // arrived on after the stores), so its consumers can be told.  One system-scope fence covers
+      // up to four tiles: the fence waits for the peers' write acknowledgements, and this warp also
+      // feeds the TMA pipeline.
+      if (loader_flags) {
+        const uint32_t stored = t_stage == kNoTile ? k : (k >= (uint32_t)NS ? k - NS + 1 : 0u);  // tiles [0, stored) are out
+        if (t_stage == kNoTile)
+          for (uint32_t j = flagged > (k >= (uint32_t)NS ? k - NS + 1 : 0u) ? flagged : (k >= (uint32_t)NS ? k - NS + 1 : 0u); j < k; ++j)
+            wait_or_flag(&sh.moved[j % NS], (j / NS) & 1, ws, abort);  // the last tiles: no stage_free to lean on
+        if (stored - flagged >= 4 || (t_stage == kNoTile && stored > flagged)) {
+          fence_acq_rel_sys();
+          for (uint32_t j = flagged; j < stored; ++j) {
+            const Seg v = seg_of(sh.tile[j & 7]);
+            if ((uint32_t)lane < dst_count(v)) {
+              uint32_t* flags = p.out_ready[dst_first(v) + lane];
+              if (flags) st_relaxed_sys_u32(flags + v.lt, sh.ok_ring[j & 7] ? p.ring_epoch : 0xffffffffu);
+            }
+          }
+          flagged = stored;
+        }
+      }
       if (t_stage == kNoTile) break;
       if (kHasIn)
         for (uint32_t q = 2; q < Q; ++q) stage_job(q);
@@ -318,16 +327,12 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
     // ================================ scanner warp ===============================================
     // runs the decoupled look-back of the output stream as soon as a tile's total is known, while
     // the compute warps are still transposing and packing; hands them the tile's global offset
-    const bool collective = p.out_ready[0] != nullptr;
     for (uint32_t k = 0;; ++k) {
       const int s = k % NS;
       const uint32_t par = (k / NS) & 1;
       if (!wait_or_flag(&sh.scan_done[s], par, ws, abort)) break;
       const uint32_t tile = sh.tile[k & 7];
-      if (tile == kNoTile) {
-        if (collective && kLag && k >= 1) raise_flags(k - 1);  // the tile that left one turn late
-        break;
-      }
+      if (tile == kNoTile) break;
       const Seg v = seg_of(tile);
       const uint32_t tot = sh.out_tot[s];
       bool ok = true;
@@ -341,12 +346,11 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       if (lane == 0) {
         sh.out_base[s] = goff;
         sh.out_ok[s] = ok ? 1u : 0u;
+        sh.ok_ring[k & 7] = ok ? 1u : 0u;
         mbar_arrive(&sh.base_ready[s]);
         if (ok && v.lt == p.tiles_per_seg - 1 && p.size_out) p.size_out[v.g] = goff + tot;
         if (fatal_error(ws.ctrl)) *abort = 1;
       }
-      __syncwarp();
-      if (collective && k >= (uint32_t)kLag) raise_flags(k - kLag);
     }
   } else {
     // ================================ compute warps ==============================================
