@@ -144,7 +144,7 @@ int hc_hom_add_stream(hc_codec* c, const uint8_t* d_a, size_t a_size, const uint
 }
 
 static int decompress_call(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, float eb, int mode, float* d_x,
-                           const uint32_t* d_tile_flags, uint32_t want, hc_stream_t stream) {
+                           const uint64_t* d_tile_flags, uint32_t want, hc_stream_t stream) {
   if (int rc = check_call(c, n, eb, true)) return rc;
   if (mode < 0 || mode > 2 || !d_in || !d_x) return hc::kErrArgument;
   if (n == 0) return hc::kOk;
@@ -168,8 +168,8 @@ int hc_decompress(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, fl
 }
 
 int hc_decompress_flagged(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, float eb, int mode, float* d_x,
-                          const uint32_t* d_tile_flags, uint32_t want, hc_stream_t stream) {
-  if (!d_tile_flags) return hc::kErrArgument;
+                          const uint64_t* d_tile_flags, uint32_t want, hc_stream_t stream) {
+  if (!d_tile_flags || want == 0 || want > 0xffffffu) return hc::kErrArgument;
   return decompress_call(c, d_in, in_size, n, eb, mode, d_x, d_tile_flags, want, stream);
 }
 

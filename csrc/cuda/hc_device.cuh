@@ -104,6 +104,22 @@ __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
 __device__ __forceinline__ void st_relaxed_sys_u32(uint32_t* p, uint32_t v) {
   asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ uint64_t ld_acquire_sys_u64(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_sys_u64(uint64_t* p, uint64_t v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// Arrival flag of a tile in a collective step: [63:40] call number, [39:0] byte offset of the tile's
+// payload in the stream (all ones = the producer gave up on the tile).  Carrying the offset lets the
+// consumer stage the tile without walking the stream's look-back chain again.
+constexpr uint64_t kFlagOffsetMask = (1ull << 40) - 1;
+__device__ __forceinline__ uint64_t flag_pack(uint32_t call, uint64_t offset) {
+  return ((uint64_t)(call & 0xffffffu) << 40) | (offset & kFlagOffsetMask);
+}
+__device__ __forceinline__ bool flag_matches(uint64_t w, uint32_t call) { return (uint32_t)(w >> 40) == (call & 0xffffffu); }
 __device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ uint4 ld_cg_u4(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
 __device__ __forceinline__ uint32_t ld_cg_u8(const uint8_t* p) { return (uint32_t)__ldcg(p); }

@@ -27,6 +27,7 @@ struct __align__(16) EncShared {
   uint32_t out_tot[kMaxStages];     // payload bytes of the tile in stage s
   uint32_t out_ok[kMaxStages];
   uint32_t ok_ring[8];              // out_ok by ticket ring slot (flags may be raised several tiles late)
+  uint64_t base_ring[8];            // out_base by ticket ring slot
   uint64_t out_base[kMaxStages];    // global byte offset of the tile's payload
   uint32_t wsum[2][kComputeThreads / 32];
   uint32_t abort;
@@ -84,7 +85,8 @@ __device__ __forceinline__ void loader_stage_stream(const uint8_t* in, uint64_t 
                                                     const Chain& st, const Workspace& ws, uint8_t* cbuf, uint64_t* full,
                                                     uint16_t* s_rel, uint8_t* s_rate, uint32_t* s_phase, bool usable,
                                                     const uint32_t (&rate_in)[kRatesPerLane], uint64_t* free_bar,
-                                                    uint32_t free_parity, bool wait_free, volatile uint32_t* abort) {
+                                                    uint32_t free_parity, bool wait_free, volatile uint32_t* abort,
+                                                    bool base_known = false, uint64_t base_given = 0) {
   const int lane = threadIdx.x & 31;
   constexpr int kPer = kRatesPerLane;
   uint32_t rate[kPer], len[kPer], sum = 0;
@@ -96,10 +98,11 @@ __device__ __forceinline__ void loader_stage_stream(const uint8_t* in, uint64_t 
   }
   const uint32_t inc = warp_inclusive_scan(sum, lane);
   const uint32_t tot = __shfl_sync(0xffffffffu, inc, 31);
-  bool ok;
-  const uint64_t excl = lookback(st, tile, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
+  // collective steps: the producer's arrival flag carries the tile's byte offset, no look-back
+  bool ok = true;
+  uint64_t base = base_given;
+  if (!base_known) base = nrate + lookback(st, tile, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
   ok = ok && usable;
-  const uint64_t base = nrate + excl;
   if (ok && base + tot > in_size) {  // stream shorter than its rate bytes imply
     if (lane == 0) note_error(ws.ctrl, kErrTruncated);
     ok = false;
@@ -129,20 +132,23 @@ __device__ __forceinline__ void loader_stage_stream(const uint8_t* in, uint64_t 
   }
 }
 
-// ring steps: has the tile's arrival flag been raised yet? (one non-blocking look)
-__device__ __forceinline__ bool flag_is_up(const uint32_t* flag, uint32_t want) {
-  uint32_t up = 0;
-  if ((threadIdx.x & 31) == 0) up = ld_acquire_sys_u32(flag) == want ? 1u : 0u;
-  return __shfl_sync(0xffffffffu, up, 0) != 0;
-}
-// ring steps: bounded wait for the tile's arrival flag; false = the peer never delivered
-__device__ __forceinline__ bool flag_wait_warp(const uint32_t* flag, uint32_t want, const Workspace& ws) {
-  uint32_t okf = 1;
+// collective steps: one non-blocking look at the tile's arrival flag; 0 = not raised yet
+__device__ __forceinline__ uint64_t flag_peek(const uint64_t* flag, uint32_t call) {
+  uint64_t w = 0;
   if ((threadIdx.x & 31) == 0) {
-    okf = wait_flag(flag, want, ws.spin_limit_ns, ws.ctrl + 2) ? 1u : 0u;
-    if (!okf) note_error(ws.ctrl, kErrPeer);
+    w = ld_acquire_sys_u64(flag);
+    if (!flag_matches(w, call)) w = 0;
   }
-  return __shfl_sync(0xffffffffu, okf, 0) != 0;
+  return __shfl_sync(0xffffffffu, w, 0);
+}
+// collective steps: bounded wait for the tile's arrival flag; 0 = the peer never delivered
+__device__ __forceinline__ uint64_t flag_wait_warp(const uint64_t* flag, uint32_t call, const Workspace& ws) {
+  uint64_t w = 0;
+  if ((threadIdx.x & 31) == 0) {
+    w = wait_tile_flag(flag, call, ws.spin_limit_ns, ws.ctrl + 2);
+    if (w == 0) note_error(ws.ctrl, kErrPeer);
+  }
+  return __shfl_sync(0xffffffffu, w, 0);
 }
 
 // Shared-memory plan of the stream-producing kernel (offsets from a 1024-byte aligned base):
@@ -239,9 +245,11 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       t = __shfl_sync(0xffffffffu, t, 0);
       return t < p.n_tiles ? t : kNoTile;
     };
-    auto try_fetch = [&](uint32_t t, uint32_t q, uint32_t (&r)[kRatesPerLane]) -> bool {  // non-blocking
+    // non-blocking; fw receives the tile's arrival flag word when the stream has flags
+    auto try_fetch = [&](uint32_t t, uint32_t q, uint32_t (&r)[kRatesPerLane], uint64_t& fw) -> bool {
       if (!kHasIn || t == kNoTile) return false;
-      if (p.in_ready[q] && !flag_is_up(p.in_ready[q] + t, p.ring_epoch)) return false;
+      fw = 0;
+      if (p.in_ready[q] && (fw = flag_peek(p.in_ready[q] + t, p.ring_epoch)) == 0) return false;
       loader_fetch_rates(p.in[q], p.in_size[q], t, r);
       return true;
     };
@@ -250,7 +258,8 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
     uint32_t tile = take();
     uint32_t tile_n = tile != kNoTile ? take() : kNoTile;
     uint32_t rates[kRatesPerLane] = {}, rates_n[kRatesPerLane] = {};
-    bool have = try_fetch(tile, 0, rates), have_n = false;
+    uint64_t fw = 0, fw_n = 0;  // arrival flag words that came with the prefetched rate bytes
+    bool have = try_fetch(tile, 0, rates, fw), have_n = false;
     for (uint32_t k = 0;; ++k) {
       const int s = k % NS, slot = k & 7;
       const uint32_t tile_nn = (tile != kNoTile && tile_n != kNoTile) ? take() : kNoTile;
@@ -260,16 +269,21 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
         const uint32_t v = k * Q + q, b = v & 1u, u = v >> 1;
         // next staging job: the next stream of this tile, or the first stream of the next tile
         const bool last_q = q + 1 == Q;
-        have_n = try_fetch(last_q ? tile_n : tile, last_q ? 0u : q + 1, rates_n);
+        have_n = try_fetch(last_q ? tile_n : tile, last_q ? 0u : q + 1, rates_n, fw_n);
         bool usable = true;
         if (!have) {
-          if (p.in_ready[q] && !flag_wait_warp(p.in_ready[q] + tile, p.ring_epoch, ws)) usable = false;
+          fw = 0;
+          if (p.in_ready[q] && (fw = flag_wait_warp(p.in_ready[q] + tile, p.ring_epoch, ws)) == 0) usable = false;
           if (usable) loader_fetch_rates(p.in[q], p.in_size[q], tile, rates);
         }
+        const bool flagged_in = p.in_ready[q] != nullptr;
+        if (flagged_in && (fw & kFlagOffsetMask) == kFlagOffsetMask) usable = false;  // the producer gave up
         const Chain chain{ws.st_a + (size_t)q * p.tiles_per_seg, ws.grp_a + (size_t)q * groups_per_seg};
         loader_stage_stream(p.in[q], p.in_size[q], nrate, tile, chain, ws, cbuf[b], &sh.in_full[b], sh.in_rel[b],
-                            sh.in_rate[b], &sh.in_phase[b], usable, rates, &sh.in_free[b], (u - 1) & 1, u >= 1, abort);
+                            sh.in_rate[b], &sh.in_phase[b], usable, rates, &sh.in_free[b], (u - 1) & 1, u >= 1, abort,
+                            flagged_in, fw & kFlagOffsetMask);
         have = have_n;
+        fw = fw_n;
 #pragma unroll
         for (int i = 0; i < kRatesPerLane; ++i) rates[i] = rates_n[i];
       };
@@ -310,8 +324,10 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
           for (uint32_t j = flagged; j < stored; ++j) {
             const Seg v = seg_of(sh.tile[j & 7]);
             if ((uint32_t)lane < dst_count(v)) {
-              uint32_t* flags = p.out_ready[dst_first(v) + lane];
-              if (flags) st_relaxed_sys_u32(flags + v.lt, sh.ok_ring[j & 7] ? p.ring_epoch : 0xffffffffu);
+              uint64_t* flags = p.out_ready[dst_first(v) + lane];
+              if (flags)
+                st_relaxed_sys_u64(flags + v.lt,
+                                   flag_pack(p.ring_epoch, sh.ok_ring[j & 7] ? sh.base_ring[j & 7] : kFlagOffsetMask));
             }
           }
           flagged = stored;
@@ -347,6 +363,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
         sh.out_base[s] = goff;
         sh.out_ok[s] = ok ? 1u : 0u;
         sh.ok_ring[k & 7] = ok ? 1u : 0u;
+        sh.base_ring[k & 7] = goff;
         mbar_arrive(&sh.base_ready[s]);
         if (ok && v.lt == p.tiles_per_seg - 1 && p.size_out) p.size_out[v.g] = goff + tot;
         if (fatal_error(ws.ctrl)) *abort = 1;
@@ -508,18 +525,21 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
       t = __shfl_sync(0xffffffffu, t, 0);
       return t < p.n_tiles ? t : kNoTile;
     };
-    auto try_fetch = [&](uint32_t t, uint32_t (&r)[kRatesPerLane]) -> bool {  // non-blocking
+    // non-blocking; fw receives the tile's arrival flag word when the segment has flags
+    auto try_fetch = [&](uint32_t t, uint32_t (&r)[kRatesPerLane], uint64_t& fw) -> bool {
       if (t == kNoTile) return false;
       const uint32_t sg = t / p.tiles_per_seg, lt = t - sg * p.tiles_per_seg;
       const DecSegment& seg = p.seg[sg];
-      if (seg.in_ready && !flag_is_up(seg.in_ready + lt, p.ring_epoch)) return false;
+      fw = 0;
+      if (seg.in_ready && (fw = flag_peek(seg.in_ready + lt, p.ring_epoch)) == 0) return false;
       loader_fetch_rates(seg.in, seg.in_size, lt, r);
       return true;
     };
     uint32_t tile = take();
     uint32_t tile_n = tile != kNoTile ? take() : kNoTile;
     uint32_t rates[kRatesPerLane] = {}, rates_n[kRatesPerLane] = {};
-    bool have = try_fetch(tile, rates), have_n = false;
+    uint64_t fw = 0, fw_n = 0;
+    bool have = try_fetch(tile, rates, fw), have_n = false;
     for (uint32_t k = 0;; ++k) {
       const int s = k & 1;
       if (tile == kNoTile) {
@@ -531,23 +551,27 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
         break;
       }
       const uint32_t tile_nn = tile_n != kNoTile ? take() : kNoTile;
-      have_n = try_fetch(tile_n, rates_n);
+      have_n = try_fetch(tile_n, rates_n, fw_n);
       const uint32_t sg = tile / p.tiles_per_seg, lt = tile - sg * p.tiles_per_seg;
       const DecSegment& seg = p.seg[sg];
       bool usable = true;
       if (!have) {
-        if (seg.in_ready && !flag_wait_warp(seg.in_ready + lt, p.ring_epoch, ws)) usable = false;
+        fw = 0;
+        if (seg.in_ready && (fw = flag_wait_warp(seg.in_ready + lt, p.ring_epoch, ws)) == 0) usable = false;
         if (usable) loader_fetch_rates(seg.in, seg.in_size, lt, rates);
       }
+      const bool flagged_in = seg.in_ready != nullptr;
+      if (flagged_in && (fw & kFlagOffsetMask) == kFlagOffsetMask) usable = false;  // the producer gave up
       const Chain chain{ws.st_a + (size_t)sg * p.tiles_per_seg, ws.grp_a + (size_t)sg * groups_per_seg};
       if (lane == 0) sh.tile[k & 3] = tile;  // ring of 4 > 2 buffers: nobody still reads this slot
       loader_stage_stream(seg.in, seg.in_size, rate_bytes(seg.n), lt, chain, ws, cbuf[s], &sh.in_full[s], sh.in_rel[s],
                           sh.in_rate[s], &sh.in_phase[s], usable, rates, &sh.in_free[s], ((k >> 1) - 1) & 1, k >= 2,
-                          abort);
+                          abort, flagged_in, fw & kFlagOffsetMask);
       if (lane == 0 && fatal_error(ws.ctrl)) *abort = 1;
       tile = tile_n;
       tile_n = tile_nn;
       have = have_n;
+      fw = fw_n;
 #pragma unroll
       for (int i = 0; i < kRatesPerLane; ++i) rates[i] = rates_n[i];
     }

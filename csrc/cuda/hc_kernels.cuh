@@ -77,11 +77,11 @@ struct EncParams {
   float recip;       // 0.5f / eb
   const uint8_t* in[kMaxIn];
   uint64_t in_size[kMaxIn];
-  const uint32_t* in_ready[kMaxIn];  // one arrival flag per tile, or null
+  const uint64_t* in_ready[kMaxIn];  // one arrival flag per tile (dev::flag_pack), or null
   uint32_t ring_epoch;
   uint32_t n_dst;                // destinations of the single segment (ignored when n_seg > 1)
   uint8_t* out[kMaxDst];         // n_seg == 1: destinations; n_seg > 1: out[g] of segment g
-  uint32_t* out_ready[kMaxDst];  // arrival flags on the consumers, laid out like `out`, or null
+  uint64_t* out_ready[kMaxDst];  // arrival flags on the consumers, laid out like `out`, or null
   uint64_t out_cap;
   uint64_t* size_out;  // device words receiving the exact stream length of each segment (or null)
   Workspace ws;
@@ -93,7 +93,7 @@ struct EncParams {
 struct DecSegment {
   const uint8_t* in;
   uint64_t in_size;
-  const uint32_t* in_ready;  // one arrival flag per tile, or null
+  const uint64_t* in_ready;  // one arrival flag per tile (dev::flag_pack), or null
   float* out;
   uint64_t n;
   uint32_t use_tma;
@@ -495,7 +495,7 @@ __device__ __forceinline__ uint64_t lookback(const Chain& ch, uint32_t tile, uin
   return excl;
 }
 
-// bounded wait for an arrival flag written by another GPU
+// bounded wait for a 32-bit flag written by another GPU (uncompressed collective)
 __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, uint64_t limit_ns, volatile uint32_t* err_word) {
   if (ld_acquire_sys_u32(flag) == want) return true;
   const long long t0 = clock64();
@@ -508,6 +508,23 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, u
     }
   }
   return false;
+}
+// bounded wait for a tile's arrival flag of call `call`; returns the flag word, or 0 on time-out
+__device__ __forceinline__ uint64_t wait_tile_flag(const uint64_t* flag, uint32_t call, uint64_t limit_ns,
+                                                   volatile uint32_t* err_word) {
+  uint64_t w = ld_acquire_sys_u64(flag);
+  if (flag_matches(w, call)) return w;
+  const long long t0 = clock64();
+  const long long limit_clk = (long long)limit_ns * 2;
+  for (uint32_t it = 0; it < (1u << 26); ++it) {
+    w = ld_acquire_sys_u64(flag);
+    if (flag_matches(w, call)) return w;
+    if ((it & 7u) == 7u) {
+      __nanosleep(64);
+      if (clock64() - t0 > limit_clk || *err_word >= (uint32_t)kErrTimeout) return 0;
+    }
+  }
+  return 0;
 }
 
 // Moves the `tot` payload bytes packed at obuf[0..tot) to global byte offset `goff` of every

@@ -14,7 +14,8 @@
 // Symmetric region of each rank (same layout everywhere):
 //   receive slots   1 .. P-1      stream written by the previous rank at its step s-1
 //   all-gather bufs [2][P]        reduced chunk c of calls with parity 0 / 1
-//   arrival flags   one uint32 per tile for every slot and buffer above, value = call number
+//   arrival flags   one uint64 per tile for every slot and buffer above: call number and the
+//                   byte offset of the tile's payload, so consumers never re-derive offsets
 // Flags carry the call number, so nothing is ever reset; all-gather buffers alternate between two
 // sets because a fast rank may start pushing call n+1 while a slow one still decodes call n.
 #include <new>
@@ -41,7 +42,7 @@ struct Layout {
     world = P;
     chunk_max = hc_chunk_elems(max_count, P);
     slot_bytes = round_up(hc::max_stream_bytes(chunk_max) + 64, kAlign);
-    flag_bytes = round_up((hc::rate_bytes(chunk_max) / hc::kTileBlocks + 1) * sizeof(uint32_t), kAlign);
+    flag_bytes = round_up((hc::rate_bytes(chunk_max) / hc::kTileBlocks + 1) * sizeof(uint64_t), kAlign);
     n_slots = (size_t)(P - 1) + 2 * (size_t)P;
     flags_off = n_slots * slot_bytes;
     raw_flags_off = flags_off + n_slots * flag_bytes;
@@ -190,7 +191,7 @@ static int allreduce_ring(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t
     return (hi > count ? count : hi) - lo;
   };
   c->call += 1;
-  if (c->call == 0) c->call = 1;  // 0 means "never written"
+  if ((c->call & 0xffffffu) == 0) c->call += 1;  // flags carry 24 bits of it; 0 means "never written"
   const uint32_t call = c->call;
   const int parity = (int)(call & 1u);
   const int next = (r + 1) % P;
@@ -220,13 +221,13 @@ static int allreduce_ring(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t
       p.n_in = 1;
       p.in[0] = self + L.data_off(slot);
       p.in_size[0] = L.slot_bytes;
-      p.in_ready[0] = reinterpret_cast<const uint32_t*>(self + L.flag_off(slot));
+      p.in_ready[0] = reinterpret_cast<const uint64_t*>(self + L.flag_off(slot));
     }
     if (s < P - 1) {
       const size_t slot = L.rs_slot(s + 1);
       p.n_dst = 1;
       p.out[0] = c->peer[next] + L.data_off(slot);
-      p.out_ready[0] = reinterpret_cast<uint32_t*>(c->peer[next] + L.flag_off(slot));
+      p.out_ready[0] = reinterpret_cast<uint64_t*>(c->peer[next] + L.flag_off(slot));
     } else {
       // reduced chunk: to the all-gather buffer of every rank, own copy first
       const size_t slot = L.ag_slot(parity, ch);
@@ -234,7 +235,7 @@ static int allreduce_ring(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t
       for (int k = 0; k < P; ++k) {
         const int dst = (r + k) % P;
         p.out[k] = c->peer[dst] + L.data_off(slot);
-        p.out_ready[k] = reinterpret_cast<uint32_t*>(c->peer[dst] + L.flag_off(slot));
+        p.out_ready[k] = reinterpret_cast<uint64_t*>(c->peer[dst] + L.flag_off(slot));
       }
     }
     p.ws = next_ws(c, stream);
@@ -257,7 +258,7 @@ static int allreduce_ring(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t
     hc::DecSegment& sg = d.seg[d.n_seg++];
     sg.in = self + L.data_off(slot);
     sg.in_size = L.slot_bytes;
-    sg.in_ready = reinterpret_cast<const uint32_t*>(self + L.flag_off(slot));
+    sg.in_ready = reinterpret_cast<const uint64_t*>(self + L.flag_off(slot));
     sg.out = d_rbuf + (size_t)ch * B;
     sg.n = n;
   }
@@ -291,7 +292,7 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
     return (hi > count ? count : hi) - lo;
   };
   c->call += 1;
-  if (c->call == 0) c->call = 1;
+  if ((c->call & 0xffffffu) == 0) c->call += 1;  // flags carry 24 bits of it; 0 means "never written"
   const uint32_t call = c->call;
   const int parity = (int)(call & 1u);
   uint8_t* self = c->peer[r];
@@ -317,7 +318,7 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
       p.local[g] = d_sbuf + (size_t)d * B;
       p.n[g] = n;
       p.out[g] = c->peer[d] + L.data_off(slot);
-      p.out_ready[g] = reinterpret_cast<uint32_t*>(c->peer[d] + L.flag_off(slot));
+      p.out_ready[g] = reinterpret_cast<uint64_t*>(c->peer[d] + L.flag_off(slot));
     }
     if (p.n_seg) {
       p.n_dst = 1;
@@ -342,14 +343,14 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
       const uint32_t q = p.n_in++;
       p.in[q] = self + L.data_off(slot);
       p.in_size[q] = L.slot_bytes;
-      p.in_ready[q] = reinterpret_cast<const uint32_t*>(self + L.flag_off(slot));
+      p.in_ready[q] = reinterpret_cast<const uint64_t*>(self + L.flag_off(slot));
     }
     const size_t slot = L.ag_slot(parity, r);
     p.n_dst = (uint32_t)P;
     for (int k = 0; k < P; ++k) {
       const int dst = (r + k) % P;
       p.out[k] = c->peer[dst] + L.data_off(slot);
-      p.out_ready[k] = reinterpret_cast<uint32_t*>(c->peer[dst] + L.flag_off(slot));
+      p.out_ready[k] = reinterpret_cast<uint64_t*>(c->peer[dst] + L.flag_off(slot));
     }
     p.ws = next_ws(c, stream);
     if (hc::launch_encode(P > 1 ? hc::kOpAddF32 : hc::kOpCompress, hc::kModeOutlier, p, stream) != cudaSuccess)
@@ -369,7 +370,7 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
     hc::DecSegment& sg = d.seg[d.n_seg++];
     sg.in = self + L.data_off(slot);
     sg.in_size = L.slot_bytes;
-    sg.in_ready = reinterpret_cast<const uint32_t*>(self + L.flag_off(slot));
+    sg.in_ready = reinterpret_cast<const uint64_t*>(self + L.flag_off(slot));
     sg.out = d_rbuf + (size_t)ch * B;
     sg.n = n;
   }

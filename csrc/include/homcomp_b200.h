@@ -71,12 +71,15 @@ int hc_compress(hc_codec* c, const float* d_x, size_t n, float eb, int mode, uin
                 uint64_t* d_size, hc_stream_t stream);
 int hc_decompress(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, float eb, int mode, float* d_x,
                   hc_stream_t stream);
-// Streaming decode: the stream is being written by another producer (another stream, another GPU);
-// d_tile_flags holds one uint32 per tile of hc_tile_elems() values, and tile t is decoded once
-// d_tile_flags[t] == want (acquire at system scope).  A flag that never rises ends in status 6
-// (peer) after the handle's timeout; the kernel always runs to its end.
+// Streaming decode: the stream is being written by another producer (another stream, another GPU).
+// d_tile_flags holds one uint64 per tile of hc_tile_elems() values; tile t is decoded once the
+// producer has stored (with release semantics at system scope)
+//     d_tile_flags[t] = ((uint64_t)want << 40) | byte offset of the tile's payload in the stream
+// where want is a non-zero 24-bit tag of the producer's choice (an offset field of all ones marks a
+// tile the producer gave up on).  A flag that never rises ends in status 6 (peer) after the
+// handle's timeout; the kernel always runs to its end.
 int hc_decompress_flagged(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, float eb, int mode, float* d_x,
-                          const uint32_t* d_tile_flags, uint32_t want, hc_stream_t stream);
+                          const uint64_t* d_tile_flags, uint32_t want, hc_stream_t stream);
 size_t hc_tile_elems(void);
 int hc_hom_add_f32(hc_codec* c, const uint8_t* d_in, size_t in_size, const float* d_local, size_t n, float eb,
                    int mode, uint8_t* d_out, size_t cap, uint64_t* d_size, hc_stream_t stream);

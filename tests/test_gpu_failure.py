@@ -18,11 +18,21 @@ def test_flag_that_never_rises_times_out_with_status():
     gs = torch.from_numpy(np.concatenate([s, np.zeros(64, np.uint8)])).cuda()
     codec = ops.Codec(n, timeout_ms=300)
     tiles = (ops.rate_bytes(n) * 32) // codec.tile_elems
-    flags = torch.zeros(tiles, dtype=torch.int32, device="cuda")
-    # producer "arrived" for the first tiles only; nothing ever sets the rest
-    flags[:3] = 7
+    # what a producer would publish: tag << 40 | byte offset of the tile's payload
+    rate = s[: ops.rate_bytes(n)].astype(np.int64)
+    F, outl = rate & 31, rate >> 7
+    plen = np.where(outl == 1, 4 + 4 * F + ((rate >> 5) & 3) + 1, np.where(F > 0, 4 + 4 * F, 0))
+    per_tile = plen.reshape(tiles, -1).sum(axis=1)
+    offs = ops.rate_bytes(n) + np.concatenate([[0], np.cumsum(per_tile)[:-1]])
+
+    def flags_for(tag, upto):
+        f = np.zeros(tiles, dtype=np.int64)
+        f[:upto] = (tag << 40) | offs[:upto]
+        return torch.from_numpy(f).cuda()
+
+    # the producer "arrived" for the first tiles only; nothing ever sets the rest
     t0 = time.time()
-    y = codec.decompress_flagged(gs, n, eb, flags, want=7, stream_bytes=s.size)
+    y = codec.decompress_flagged(gs, n, eb, flags_for(7, 3), want=7, stream_bytes=s.size)
     status = codec.status()
     assert status == 6  # peer never delivered
     assert time.time() - t0 < 20  # bounded, not a hang
@@ -30,8 +40,7 @@ def test_flag_that_never_rises_times_out_with_status():
     done = 3 * codec.tile_elems
     np.testing.assert_array_equal(y[:done].cpu().numpy(), want[:done])  # delivered tiles were decoded
     # all flags up: the same handle works again
-    flags.fill_(9)
-    y = codec.decompress_flagged(gs, n, eb, flags, want=9, stream_bytes=s.size)
+    y = codec.decompress_flagged(gs, n, eb, flags_for(9, tiles), want=9, stream_bytes=s.size)
     assert codec.status() == 0
     np.testing.assert_array_equal(y.cpu().numpy(), want)
 

@@ -91,7 +91,8 @@ class Codec:
 
     def decompress_flagged(self, stream: torch.Tensor, n: int, eb: float, tile_flags: torch.Tensor, want: int,
                            mode="outlier", out=None, stream_bytes=None):
-        """Decode tile by tile as ``tile_flags[t] == want`` (uint32/int32, one per ``tile_elems`` values)."""
+        """Decode tile by tile as the producer publishes ``tile_flags[t] = want << 40 | payload offset``
+        (int64, one word per ``tile_elems`` values; ``want`` is a non-zero 24-bit tag)."""
         if out is None:
             out = torch.empty(n, dtype=torch.float32, device=self.device)
         nbytes = stream.numel() if stream_bytes is None else int(stream_bytes)
