@@ -120,6 +120,13 @@ __device__ __forceinline__ uint64_t flag_pack(uint32_t call, uint64_t offset) {
   return ((uint64_t)(call & 0xffffffu) << 40) | (offset & kFlagOffsetMask);
 }
 __device__ __forceinline__ bool flag_matches(uint64_t w, uint32_t call) { return (uint32_t)(w >> 40) == (call & 0xffffffu); }
+// One 16-byte store that NVSwitch replicates into every GPU bound to the multicast object behind
+// `mc_addr` (an address inside a multicast mapping; such addresses take multimem instructions only).
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(a)),
+               "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
+               : "memory");
+}
 __device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ uint4 ld_cg_u4(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
 __device__ __forceinline__ uint32_t ld_cg_u8(const uint8_t* p) { return (uint32_t)__ldcg(p); }

@@ -228,7 +228,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
     const Seg v = seg_of(sh.tile[j & 7]);
     if (sh.out_ok[sj])
       copy_out(stage0 + sj * kStagePitch, p.out + dst_first(v), dst_count(v), sh.out_base[sj], sh.out_tot[sj], tid,
-               kComputeThreads);
+               kComputeThreads, p.n_seg == 1 ? p.out_mc : nullptr);
     mbar_arrive(&sh.moved[sj]);       // the loader raises the consumers' arrival flags (collective steps)
     mbar_arrive(&sh.stage_free[sj]);  // the loader may refill the stage
   };

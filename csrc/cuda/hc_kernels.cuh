@@ -82,6 +82,7 @@ struct EncParams {
   uint32_t n_dst;                // destinations of the single segment (ignored when n_seg > 1)
   uint8_t* out[kMaxDst];         // n_seg == 1: destinations; n_seg > 1: out[g] of segment g
   uint64_t* out_ready[kMaxDst];  // arrival flags on the consumers, laid out like `out`, or null
+  uint8_t* out_mc;               // n_seg == 1 only: multicast alias of all n_dst destinations (NVLS), or null
   uint64_t out_cap;
   uint64_t* size_out;  // device words receiving the exact stream length of each segment (or null)
   Workspace ws;
@@ -531,8 +532,10 @@ __device__ __forceinline__ uint64_t wait_tile_flag(const uint64_t* flag, uint32_
 // destination, with aligned 16-byte stores wherever a whole unit belongs to this tile (run by
 // `nthr` threads, this one being number `t`).  16 readable guard bytes must precede and follow
 // obuf.  All destinations share the same 16-byte phase.
+// `mc` (optional): multicast alias of ALL n_dst destinations; whole 16-byte units then leave with one
+// multimem store instead of n_dst peer stores, the ragged first/last unit still goes to each peer.
 __device__ __forceinline__ void copy_out(const uint8_t* obuf, uint8_t* const* outs, uint32_t n_dst, uint64_t goff,
-                                         uint32_t tot, uint32_t t, uint32_t nthr) {
+                                         uint32_t tot, uint32_t t, uint32_t nthr, uint8_t* mc = nullptr) {
   if (tot == 0) return;
   const uint32_t phase = (uint32_t)((reinterpret_cast<uintptr_t>(outs[0]) + goff) & 15u);
   const uint32_t nvec = (phase + tot + 15u) >> 4;
@@ -546,6 +549,10 @@ __device__ __forceinline__ void copy_out(const uint8_t* obuf, uint8_t* const* ou
                      __funnelshift_r(w3, w4, sh)};
     const uint32_t lo = 16u * v, hi = lo + 16u;
     const bool full = lo >= lo_valid && hi <= hi_valid;
+    if (full && mc != nullptr) {
+      multimem_st_v4(mc + goff - phase + lo, o[0], o[1], o[2], o[3]);
+      continue;
+    }
 #pragma unroll 1
     for (uint32_t d = 0; d < n_dst; ++d) {
       uint8_t* p = outs[d] + goff - phase + lo;

@@ -237,6 +237,7 @@ static int allreduce_ring(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t
         p.out[k] = c->peer[dst] + L.data_off(slot);
         p.out_ready[k] = reinterpret_cast<uint64_t*>(c->peer[dst] + L.flag_off(slot));
       }
+      if (c->mc && P > 1) p.out_mc = c->mc + L.data_off(slot);  // one multimem store reaches all P copies
     }
     p.ws = next_ws(c, stream);
     if (hc::launch_encode(s == 0 ? hc::kOpCompress : hc::kOpAddF32, hc::kModeOutlier, p, stream) != cudaSuccess)
@@ -352,6 +353,7 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
       p.out[k] = c->peer[dst] + L.data_off(slot);
       p.out_ready[k] = reinterpret_cast<uint64_t*>(c->peer[dst] + L.flag_off(slot));
     }
+    if (c->mc && P > 1) p.out_mc = c->mc + L.data_off(slot);  // one multimem store reaches all P copies
     p.ws = next_ws(c, stream);
     if (hc::launch_encode(P > 1 ? hc::kOpAddF32 : hc::kOpCompress, hc::kModeOutlier, p, stream) != cudaSuccess)
       return hc::kErrCuda;

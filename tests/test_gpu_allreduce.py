@@ -82,3 +82,47 @@ def test_uncompressed_and_named_variants():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     run_ranks(_raw_worker, 2)
+
+
+def _nvls_worker(rank, world, counts, eb, note_path):
+    """Same check over the multicast transport.  Mismatches are collected and raised only after
+    every rank has left the collective and unmapped its region together."""
+    import torch.distributed as dist
+
+    from datasets import gradient_like, smooth
+    from tirocinio_triennale_b200 import ops
+    from tirocinio_triennale_b200.parallel import CompressedAllreduce
+
+    ar = CompressedAllreduce(max(counts), timeout_ms=5000, transport="nvls")
+    problems = []
+    for algorithm in ("direct", "ring"):
+        ar.set_algorithm(algorithm)
+        for it, n in enumerate(counts):
+            gen = smooth if it % 2 == 0 else gradient_like
+            bufs = [gen(n, seed=100 * it + r) for r in range(world)]
+            x = torch.from_numpy(bufs[rank]).cuda()
+            for rep in range(2):  # both all-gather buffer sets
+                out = torch.full_like(x, -3.0)
+                ar.allreduce(x, out, eb)
+                status = ar.status()
+                want = ops.cpu_ring_allreduce(bufs, eb)[rank]
+                if status != 0 or not np.array_equal(out.cpu().numpy(), want):
+                    problems.append((algorithm, n, rep, status))
+    multicast = ar.multicast
+    dist.barrier()
+    ar.close()
+    if rank == 0:
+        with open(note_path, "w") as f:
+            f.write("1" if multicast else "0")
+    assert not problems, problems
+
+
+def test_allreduce_over_multicast_transport(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = min(torch.cuda.device_count(), 8)
+    world = 1 << (world.bit_length() - 1)
+    note = tmp_path / "multicast"
+    run_ranks(_nvls_worker, world, args=([1, 4097, 100000, (1 << 22) + 12345], 1e-4, str(note)), backend="nccl")
+    if note.read_text() != "1":
+        pytest.skip("the fabric offers no multicast mapping: ran over peer stores on symmetric memory")

@@ -23,9 +23,19 @@ class CompressedAllreduce:
     """
 
     def __init__(self, max_count: int, group=None, device=None, timeout_ms: int | None = None,
-                 algorithm: str = "direct"):
+                 algorithm: str = "direct", transport: str | None = None):
+        """``transport``: ``"ipc"`` maps every rank's region with CUDA IPC and moves all data with peer
+        stores; ``"nvls"`` takes the region from ``torch.distributed._symmetric_memory`` and, where the
+        fabric offers a multicast mapping, pushes the reduced chunk to all ranks with one
+        ``multimem.st`` per 16 bytes (falls back to peer stores on the same mapping otherwise).
+        Default: the ``HC_TRANSPORT`` environment variable, else ``"ipc"``."""
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed must be initialised (it carries the IPC handles)")
+        import os
+
+        transport = transport or os.environ.get("HC_TRANSPORT", "ipc")
+        if transport not in ("ipc", "nvls"):
+            raise ValueError("transport must be 'ipc' or 'nvls'")
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -35,26 +45,43 @@ class CompressedAllreduce:
         self._peers = {}
         self._base = None
         self._h = None
+        self._symm = None
+        self.multicast = False
         with torch.cuda.device(self.device):
             nbytes = int(self.lib.hc_comm_symmetric_bytes(self.world, self.max_count))
-            base = C.c_void_p()
-            handle = C.create_string_buffer(64)
-            _lib.check(self.lib.hc_ipc_alloc(C.byref(base), nbytes, handle), "ipc_alloc")
-            self._base = base
             self.symmetric_bytes = nbytes
-            handles = [None] * self.world
-            dist.all_gather_object(handles, bytes(handle.raw), group=group)
             ptrs = (C.c_void_p * self.world)()
-            for r in range(self.world):
-                if r == self.rank:
-                    ptrs[r] = base.value
-                else:
-                    p = C.c_void_p()
-                    _lib.check(self.lib.hc_ipc_open(handles[r], C.byref(p)), "ipc_open(rank %d)" % r)
-                    self._peers[r] = p
-                    ptrs[r] = p.value
+            mc = None
+            if transport == "nvls" and self.world > 1:
+                import torch.distributed._symmetric_memory as symm
+
+                region = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+                region.zero_()
+                hdl = symm.rendezvous(region, group if group is not None else dist.group.WORLD)
+                for r in range(self.world):
+                    ptrs[r] = int(hdl.buffer_ptrs[r])
+                if int(hdl.multicast_ptr):
+                    mc = C.c_void_p(int(hdl.multicast_ptr))
+                    self.multicast = True
+                self._symm = (region, hdl)
+            else:
+                base = C.c_void_p()
+                handle = C.create_string_buffer(64)
+                _lib.check(self.lib.hc_ipc_alloc(C.byref(base), nbytes, handle), "ipc_alloc")
+                self._base = base
+                handles = [None] * self.world
+                dist.all_gather_object(handles, bytes(handle.raw), group=group)
+                for r in range(self.world):
+                    if r == self.rank:
+                        ptrs[r] = base.value
+                    else:
+                        p = C.c_void_p()
+                        _lib.check(self.lib.hc_ipc_open(handles[r], C.byref(p)), "ipc_open(rank %d)" % r)
+                        self._peers[r] = p
+                        ptrs[r] = p.value
+            self.transport = transport
             h = C.c_void_p()
-            _lib.check(self.lib.hc_comm_create(C.byref(h), self.rank, self.world, self.max_count, ptrs, None),
+            _lib.check(self.lib.hc_comm_create(C.byref(h), self.rank, self.world, self.max_count, ptrs, mc),
                        "comm_create")
             self._h = h
             self.set_algorithm(algorithm)
@@ -130,8 +157,10 @@ class CompressedAllreduce:
             for p in self._peers.values():
                 self.lib.hc_ipc_close(p)
             self._peers = {}
-            self.lib.hc_ipc_free(self._base)
+            if self._base is not None:
+                self.lib.hc_ipc_free(self._base)
             self._base = None
+            self._symm = None
 
     def __del__(self):
         try:
