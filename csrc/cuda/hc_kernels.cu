@@ -41,6 +41,28 @@ __device__ __forceinline__ bool fatal_error(const uint32_t* ctrl) {
   return *((volatile const uint32_t*)(ctrl + 2)) >= (uint32_t)kErrTimeout;
 }
 
+// Optional per-CTA timeline (compile with -DHC_TIMELINE): sixteen nanosecond stamps of the first tile's
+// way through the roles, for finding where a launch spends its fixed time.  Not part of a normal build.
+#ifdef HC_TIMELINE
+__device__ unsigned long long g_timeline[4096 * 16];
+__device__ __forceinline__ unsigned long long timeline_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define HC_STAMP(i)                                                                  \
+  do {                                                                               \
+    if (blockIdx.x < 4096) g_timeline[blockIdx.x * 16 + (i)] = timeline_now();        \
+  } while (0)
+#define HC_STAMP_MAX(i)                                                              \
+  do {                                                                               \
+    if (blockIdx.x < 4096) atomicMax(&g_timeline[blockIdx.x * 16 + (i)], timeline_now()); \
+  } while (0)
+#else
+#define HC_STAMP(i)
+#define HC_STAMP_MAX(i)
+#endif
+
 // the last CTA to leave re-arms the ticket counter for the next launch
 __device__ __forceinline__ void cta_epilogue(uint32_t* ctrl) {
   __syncthreads();
@@ -218,6 +240,12 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
   }
   __syncthreads();
   volatile uint32_t* abort = &sh.abort;
+  if (tid == 0) {
+    HC_STAMP(0);
+#ifdef HC_TIMELINE
+    if (blockIdx.x < 4096) g_timeline[blockIdx.x * 16 + 7] = 0;
+#endif
+  }
 
   // The packed payload leaves one tile late when there are three stages (its look-back has a whole
   // tile time to finish), and in the same turn when there are two.
@@ -256,6 +284,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
     const bool loader_flags = p.out_ready[0] != nullptr;  // this launch is a step of a collective
     uint32_t flagged = 0;  // tiles [0, flagged) of this CTA have had their arrival flags raised
     uint32_t tile = take();
+    if (lane == 0) HC_STAMP(1);
     uint32_t tile_n = tile != kNoTile ? take() : kNoTile;
     uint32_t rates[kRatesPerLane] = {}, rates_n[kRatesPerLane] = {};
     uint64_t fw = 0, fw_n = 0;  // arrival flag words that came with the prefetched rate bytes
@@ -339,6 +368,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       tile = tile_n;
       tile_n = tile_nn;
     }
+    if (lane == 0) HC_STAMP(6);
   } else if (warp == kComputeThreads / 32 + 1) {
     // ================================ scanner warp ===============================================
     // runs the decoupled look-back of the output stream as soon as a tile's total is known, while
@@ -355,6 +385,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       const Chain chain{ws.st_out + (size_t)v.g * p.tiles_per_seg, ws.grp_out + (size_t)v.g * groups_per_seg};
       const uint64_t excl = lookback(chain, v.lt, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
       const uint64_t goff = v.nrate + excl;
+      if (k == 0 && lane == 0) HC_STAMP(4);
       if (ok && goff + tot > p.out_cap) {
         if (lane == 0) note_error(ws.ctrl, kErrCapacity);
         ok = false;
@@ -375,11 +406,13 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       const int s = k % NS, slot = k & 7;
       uint8_t* const stage_s = stage0 + s * kStagePitch;
       bool alive = wait_or_flag(&sh.tma_full[s], (k / NS) & 1, ws, abort);
+      if (k == 0 && tid == 0) HC_STAMP(2);
       const uint32_t tile = alive ? sh.tile[slot] : kNoTile;
       if (tile == kNoTile) {
         if (kLag && k >= 1) {
           compute_barrier();  // no scan barrier this turn: wait until every thread has packed
           move_out(k - 1);
+          if (k == 1 && tid == 0) HC_STAMP(5);
         }
         if (tid == 0) mbar_arrive(&sh.scan_done[s]);  // wakes the scanner, which sees the end marker too
         break;
@@ -405,6 +438,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
             for (int i = 0; i < 32; ++i) d[i] += d2[i];
           }
           mbar_arrive(&sh.in_free[b]);
+          if (k == 0 && tid == 0 && q < 8) HC_STAMP(8 + q);
         }
       }
 
@@ -452,6 +486,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
           st_relaxed_gpu_u64(ws.st_out + (size_t)v.g * p.tiles_per_seg + v.lt, st_pack(kStAgg, ws.epoch, tot));
         sh.out_tot[s] = tot;
         mbar_arrive(&sh.scan_done[s]);
+        if (k == 0) HC_STAMP(3);
       }
       // rate bytes (section A) go straight to every destination; a segment shorter than the longest
       // one of the launch has tickets past its own section A, which must not touch its payload
@@ -468,11 +503,14 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       if (kLag == 0) {
         compute_barrier();  // every thread's payload is packed
         move_out(k);
+        if (k == 0 && tid == 0) HC_STAMP(5);
       } else if (k >= 1) {
         move_out(k - 1);  // packed before this turn's scan barrier
+        if (k == 1 && tid == 0) HC_STAMP(5);
       }
     }
   }
+  if (lane == 0) HC_STAMP_MAX(7);
   cta_epilogue(ws.ctrl);
 }
 
@@ -514,6 +552,12 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
   }
   __syncthreads();
   volatile uint32_t* abort = &sh.abort;
+  if (tid == 0) {
+    HC_STAMP(0);
+#ifdef HC_TIMELINE
+    if (blockIdx.x < 4096) g_timeline[blockIdx.x * 16 + 7] = 0;
+#endif
+  }
 
   if (warp == kComputeThreads / 32) {
     // ================================ loader warp ================================================
@@ -536,6 +580,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
       return true;
     };
     uint32_t tile = take();
+    if (lane == 0) HC_STAMP(1);
     uint32_t tile_n = tile != kNoTile ? take() : kNoTile;
     uint32_t rates[kRatesPerLane] = {}, rates_n[kRatesPerLane] = {};
     uint64_t fw = 0, fw_n = 0;
@@ -575,11 +620,13 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
 #pragma unroll
       for (int i = 0; i < kRatesPerLane; ++i) rates[i] = rates_n[i];
     }
+    if (lane == 0) HC_STAMP(6);
   } else {
     // ================================ compute warps ==============================================
     for (uint32_t k = 0;; ++k) {
       const int s = k & 1;
       bool alive = wait_or_flag(&sh.in_full[s], (k >> 1) & 1, ws, abort);
+      if (k == 0 && tid == 0) HC_STAMP(2);
       const uint32_t tile = alive ? sh.tile[k & 3] : kNoTile;
       if (tile == kNoTile) break;
       const uint32_t sg = tile / p.tiles_per_seg, lt = tile - sg * p.tiles_per_seg;
@@ -598,6 +645,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
         for (int i = 0; i < 32; ++i) d[i] = 0;
       }
       mbar_arrive(&sh.in_free[s]);
+      if (k == 0 && tid == 0) HC_STAMP(3);
       uint32_t w[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(__fmul_rn(__fmul_rn((float)d[i], eb), 2.0f));
@@ -616,6 +664,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
         if (tma && (uint64_t)lt * kTileBlocks < full_rows)
           tma_store_2d(&tmaps.m[sg], 0, (int)(lt * kTileBlocks), obuf);
         tma_commit_group();
+        if (k == 0) HC_STAMP(5);
       }
       if (!tma || ragged) {
         const uint64_t o = row * kBlock;
@@ -626,6 +675,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
     }
     if (tid == 0) tma_wait_group<0>();
   }
+  if (lane == 0) HC_STAMP_MAX(7);
   cta_epilogue(ws.ctrl);
 }
 
@@ -882,3 +932,15 @@ cudaError_t launch_sum(float* dst, const float* a, const float* b, const float* 
 }
 
 }  // namespace hc
+
+#ifdef HC_TIMELINE
+// copies the stamps of the last launch to the host (synchronises) and clears them
+extern "C" int hc_debug_timeline(unsigned long long* host, int n_ctas) {
+  if (n_ctas > 4096) n_ctas = 4096;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(host, hc::dev::g_timeline, (size_t)n_ctas * 16 * sizeof(unsigned long long)) != cudaSuccess) return -1;
+  void* sym = nullptr;
+  if (cudaGetSymbolAddress(&sym, hc::dev::g_timeline) == cudaSuccess) cudaMemset(sym, 0, sizeof(hc::dev::g_timeline));
+  return n_ctas;
+}
+#endif
