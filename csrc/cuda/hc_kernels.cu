@@ -18,16 +18,14 @@ struct __align__(16) EncShared {
   uint64_t stage_free[kMaxStages];  // compute threads have moved the packed tile out of stage s
   uint64_t scan_done[kMaxStages];   // tile total known: the scanner may start its look-back
   uint64_t base_ready[kMaxStages];  // look-back of the tile in stage s finished: out_base / out_ok valid
-  uint64_t moved[kMaxStages];       // compute threads have stored the tile of stage s to its destinations
   uint64_t in_full[2];              // input stream bytes + meta staged in buffer b
   uint64_t in_free[2];              // compute threads have decoded from buffer b
   uint32_t tile[8];                 // ring of tile tickets, written by the loader
   uint32_t tile_tma[8];             // 1 when a TMA load was issued for that ring slot
   uint32_t in_phase[2];             // 16-byte phase of the staged bytes in buffer b
+  uint32_t in_end[2];               // 1: buffer b carries the end marker instead of a stream (ops with inputs)
   uint32_t out_tot[kMaxStages];     // payload bytes of the tile in stage s
   uint32_t out_ok[kMaxStages];
-  uint32_t ok_ring[8];              // out_ok by ticket ring slot (flags may be raised several tiles late)
-  uint64_t base_ring[8];            // out_base by ticket ring slot
   uint64_t out_base[kMaxStages];    // global byte offset of the tile's payload
   uint32_t wsum[2][kComputeThreads / 32];
   uint32_t abort;
@@ -44,23 +42,26 @@ __device__ __forceinline__ bool fatal_error(const uint32_t* ctrl) {
 // Optional per-CTA timeline (compile with -DHC_TIMELINE): sixteen nanosecond stamps of the first tile's
 // way through the roles, for finding where a launch spends its fixed time.  Not part of a normal build.
 #ifdef HC_TIMELINE
-__device__ unsigned long long g_timeline[4096 * 16];
+__device__ unsigned long long g_timeline[4 * 1024 * 16];  // [launch epoch & 3][CTA][slot]
 __device__ __forceinline__ unsigned long long timeline_now() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-#define HC_STAMP(i)                                                                  \
-  do {                                                                               \
-    if (blockIdx.x < 4096) g_timeline[blockIdx.x * 16 + (i)] = timeline_now();        \
-  } while (0)
-#define HC_STAMP_MAX(i)                                                              \
-  do {                                                                               \
-    if (blockIdx.x < 4096) atomicMax(&g_timeline[blockIdx.x * 16 + (i)], timeline_now()); \
-  } while (0)
+#define HC_TL_DECL(epoch) \
+  unsigned long long* const hc_tl = g_timeline + (((epoch)&3u) * 1024u + (blockIdx.x < 1024u ? blockIdx.x : 1023u)) * 16u
+#define HC_TL_ZERO() hc_tl[7] = hc_tl[14] = hc_tl[15] = 0
+#define HC_STAMP(i) hc_tl[i] = timeline_now()
+#define HC_STAMP_MAX(i) atomicMax(&hc_tl[i], timeline_now())
+#define HC_TIC() const unsigned long long hc_tic = timeline_now()
+#define HC_TOC(i) hc_tl[i] += timeline_now() - hc_tic
 #else
+#define HC_TL_DECL(epoch)
+#define HC_TL_ZERO()
 #define HC_STAMP(i)
 #define HC_STAMP_MAX(i)
+#define HC_TIC()
+#define HC_TOC(i)
 #endif
 
 // the last CTA to leave re-arms the ticket counter for the next launch
@@ -199,6 +200,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const Workspace& ws = p.ws;
+  HC_TL_DECL(ws.epoch);
   const uint32_t Q = kHasIn ? p.n_in : 0u;  // input streams summed into every tile
   const uint32_t groups_per_seg = p.tiles_per_seg / 32 + 1;
 
@@ -229,7 +231,6 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       mbar_init(&sh.stage_free[i], kComputeThreads);
       mbar_init(&sh.scan_done[i], 1);
       mbar_init(&sh.base_ready[i], 1);
-      mbar_init(&sh.moved[i], kComputeThreads);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sh.in_full[i], 1);
@@ -237,19 +238,18 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
     }
     fence_mbar_init();
     sh.abort = fatal_error(ws.ctrl) ? 1u : 0u;
+    HC_TL_ZERO();
+    sh.in_end[0] = sh.in_end[1] = 0u;
   }
   __syncthreads();
   volatile uint32_t* abort = &sh.abort;
-  if (tid == 0) {
-    HC_STAMP(0);
-#ifdef HC_TIMELINE
-    if (blockIdx.x < 4096) g_timeline[blockIdx.x * 16 + 7] = 0;
-#endif
-  }
+  if (tid == 0) HC_STAMP(0);
 
-  // The packed payload leaves one tile late when there are three stages (its look-back has a whole
-  // tile time to finish), and in the same turn when there are two.
-  constexpr int kLag = NS >= 3 ? 1 : 0;
+  // The packed payload of a tile leaves one turn late, so that its look-back has a whole tile time
+  // to finish: compress moves tile k-1 out at the end of turn k (three stages); the ops with input
+  // streams move it out in the middle of turn k, between decoding the inputs of tile k (which needs
+  // neither the tile's fp32 stage nor its number) and reading its local operand (two stages: the
+  // stage freed here is refilled for tile k+1 while tile k is quantised and packed).
   auto move_out = [&](uint32_t j) {  // compute threads: tile number j of this CTA -> global memory
     const int sj = j % NS;
     wait_or_flag(&sh.base_ready[sj], (j / NS) & 1, ws, abort);
@@ -257,7 +257,6 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
     if (sh.out_ok[sj])
       copy_out(stage0 + sj * kStagePitch, p.out + dst_first(v), dst_count(v), sh.out_base[sj], sh.out_tot[sj], tid,
                kComputeThreads, p.n_seg == 1 ? p.out_mc : nullptr);
-    mbar_arrive(&sh.moved[sj]);       // the loader raises the consumers' arrival flags (collective steps)
     mbar_arrive(&sh.stage_free[sj]);  // the loader may refill the stage
   };
   if (warp == kComputeThreads / 32) {
@@ -281,8 +280,6 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       loader_fetch_rates(p.in[q], p.in_size[q], t, r);
       return true;
     };
-    const bool loader_flags = p.out_ready[0] != nullptr;  // this launch is a step of a collective
-    uint32_t flagged = 0;  // tiles [0, flagged) of this CTA have had their arrival flags raised
     uint32_t tile = take();
     if (lane == 0) HC_STAMP(1);
     uint32_t tile_n = tile != kNoTile ? take() : kNoTile;
@@ -302,7 +299,9 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
         bool usable = true;
         if (!have) {
           fw = 0;
+          HC_TIC();
           if (p.in_ready[q] && (fw = flag_wait_warp(p.in_ready[q] + tile, p.ring_epoch, ws)) == 0) usable = false;
+          if (lane == 0) HC_TOC(14);
           if (usable) loader_fetch_rates(p.in[q], p.in_size[q], tile, rates);
         }
         const bool flagged_in = p.in_ready[q] != nullptr;
@@ -316,52 +315,48 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
 #pragma unroll
         for (int i = 0; i < kRatesPerLane; ++i) rates[i] = rates_n[i];
       };
-      // The first two streams go in before the tile is handed to the compute warps: their buffers
-      // only depend on earlier tiles.  Later streams reuse a buffer that the compute warps free
-      // while working on THIS tile, so they must come after the hand-over.
-      if (kHasIn && tile != kNoTile)
-        for (uint32_t q = 0; q < Q && q < 2; ++q) stage_job(q);
-      // stage s is free once the tile packed there NS turns ago has been moved out
-      uint32_t t_stage = tile;
-      if (k >= NS && !wait_or_flag(&sh.stage_free[s], ((k / NS) - 1) & 1, ws, abort)) t_stage = kNoTile;
-      if (lane == 0) {
-        sh.tile[slot] = t_stage;
-        bool fetch = false;
-        if (kHasLocal && t_stage != kNoTile) {
-          const Seg v = seg_of(t_stage);
-          fetch = p.use_tma[v.g] && (uint64_t)v.lt * kTileBlocks < v.full_rows;
-          if (fetch) {
-            fence_proxy_async();
-            mbar_expect_tx(&sh.tma_full[s], kTileBytes);
-            tma_load_2d(stage0 + s * kStagePitch, &tmaps.m[v.g], 0, (int)(v.lt * kTileBlocks), &sh.tma_full[s]);
-          }
-        }
-        sh.tile_tma[slot] = fetch ? 1u : 0u;
-        if (!fetch) mbar_arrive(&sh.tma_full[s]);
-      }
-      // compress as a collective step: every tile up to k - NS has left its stage (stage_free was
-      // arrived on after the stores), so its consumers can be told.  One system-scope fence covers
-      // up to four tiles: the fence waits for the peers' write acknowledgements, and this warp also
-      // feeds the TMA pipeline.
-      if (loader_flags) {
-        const uint32_t stored = t_stage == kNoTile ? k : (k >= (uint32_t)NS ? k - NS + 1 : 0u);  // tiles [0, stored) are out
-        if (t_stage == kNoTile)
-          for (uint32_t j = flagged > (k >= (uint32_t)NS ? k - NS + 1 : 0u) ? flagged : (k >= (uint32_t)NS ? k - NS + 1 : 0u); j < k; ++j)
-            wait_or_flag(&sh.moved[j % NS], (j / NS) & 1, ws, abort);  // the last tiles: no stage_free to lean on
-        if (stored - flagged >= 4 || (t_stage == kNoTile && stored > flagged)) {
-          fence_acq_rel_sys();
-          for (uint32_t j = flagged; j < stored; ++j) {
-            const Seg v = seg_of(sh.tile[j & 7]);
-            if ((uint32_t)lane < dst_count(v)) {
-              uint64_t* flags = p.out_ready[dst_first(v) + lane];
-              if (flags)
-                st_relaxed_sys_u64(flags + v.lt,
-                                   flag_pack(p.ring_epoch, sh.ok_ring[j & 7] ? sh.base_ring[j & 7] : kFlagOffsetMask));
+      // hand-over: the fp32 tile's TMA load into stage s (free once the tile packed there NS turns ago
+      // has been moved out) and the ticket for the compute and scanner warps
+      auto hand_over = [&]() -> uint32_t {
+        uint32_t t_stage = tile;
+        if (k >= NS && !wait_or_flag(&sh.stage_free[s], ((k / NS) - 1) & 1, ws, abort)) t_stage = kNoTile;
+        if (lane == 0) {
+          sh.tile[slot] = t_stage;
+          bool fetch = false;
+          if (kHasLocal && t_stage != kNoTile) {
+            const Seg v = seg_of(t_stage);
+            fetch = p.use_tma[v.g] && (uint64_t)v.lt * kTileBlocks < v.full_rows;
+            if (fetch) {
+              fence_proxy_async();
+              mbar_expect_tx(&sh.tma_full[s], kTileBytes);
+              tma_load_2d(stage0 + s * kStagePitch, &tmaps.m[v.g], 0, (int)(v.lt * kTileBlocks), &sh.tma_full[s]);
             }
           }
-          flagged = stored;
+          sh.tile_tma[slot] = fetch ? 1u : 0u;
+          if (!fetch) mbar_arrive(&sh.tma_full[s]);
+        }
+        return t_stage;
+      };
+      if (kHasIn && tile == kNoTile) {
+        // end of work: the compute warps look at the staging buffer first, so the marker goes there
+        const uint32_t v = k * Q, b = v & 1u, u = v >> 1;
+        if (u >= 1) wait_or_flag(&sh.in_free[b], (u - 1) & 1, ws, abort);
+        if (lane == 0) {
+          sh.tile[slot] = kNoTile;
+          sh.in_end[b] = 1u;
+          mbar_arrive(&sh.in_full[b]);
         }
       }
+      // The first NS tiles find their stage free: their TMA load goes out before anything else.
+      // Afterwards the first two input streams go in first (their buffers only depend on earlier
+      // tiles and free up before the stage does).  Later streams reuse a buffer that the compute
+      // warps free while decoding THIS tile's first streams.
+      uint32_t t_stage = kNoTile;
+      const bool early = k < (uint32_t)NS;
+      if (early) t_stage = hand_over();
+      if (kHasIn && tile != kNoTile)
+        for (uint32_t q = 0; q < Q && q < 2; ++q) stage_job(q);
+      if (!early) t_stage = hand_over();
       if (t_stage == kNoTile) break;
       if (kHasIn)
         for (uint32_t q = 2; q < Q; ++q) stage_job(q);
@@ -372,13 +367,41 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
   } else if (warp == kComputeThreads / 32 + 1) {
     // ================================ scanner warp ===============================================
     // runs the decoupled look-back of the output stream as soon as a tile's total is known, while
-    // the compute warps are still transposing and packing; hands them the tile's global offset
+    // the compute warps are still transposing and packing; hands them the tile's global offset.
+    // In a collective step it also raises the consumers' arrival flags: by the time the compute
+    // warps announce tile k's total, all of them have passed a barrier that follows the stores of
+    // tile k-1 (ops with input streams) or k-2 (compress), so those tiles can be announced.  One
+    // system-scope fence covers a batch of tiles: it waits for the peers' write acknowledgements,
+    // several microseconds over NVLink, and this warp has a tile time of slack that the loader
+    // and the compute warps do not.
+    constexpr uint32_t kFlagBatch = 4;
+    const bool raise = p.out_ready[0] != nullptr;  // this launch is a step of a collective
+    uint32_t flagged = 0;                           // tiles [0, flagged) of this CTA have been announced
+    uint32_t my_lt = 0, my_g = 0;                   // lane (j & 31) remembers this CTA's j-th tile
+    uint64_t my_word = 0;
+    auto raise_flags = [&](uint32_t upto) {  // tiles [flagged, upto) have left for their destinations
+      if (!raise || upto <= flagged) return;
+      HC_TIC();
+      fence_acq_rel_sys();
+      if (lane == 0) HC_TOC(15);
+      if (((uint32_t)lane - flagged) % 32u < upto - flagged) {
+        const uint32_t d0 = p.n_seg > 1 ? my_g : 0u, dn = p.n_seg > 1 ? 1u : p.n_dst;
+        for (uint32_t dsti = 0; dsti < dn; ++dsti) {
+          uint64_t* flags = p.out_ready[d0 + dsti];
+          if (flags) st_relaxed_sys_u64(flags + my_lt, my_word);
+        }
+      }
+      flagged = upto;
+    };
     for (uint32_t k = 0;; ++k) {
       const int s = k % NS;
       const uint32_t par = (k / NS) & 1;
       if (!wait_or_flag(&sh.scan_done[s], par, ws, abort)) break;
       const uint32_t tile = sh.tile[k & 7];
-      if (tile == kNoTile) break;
+      if (tile == kNoTile) {
+        raise_flags(k);  // the compute warps have stored every tile before they send the end marker
+        break;
+      }
       const Seg v = seg_of(tile);
       const uint32_t tot = sh.out_tot[s];
       bool ok = true;
@@ -393,40 +416,37 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       if (lane == 0) {
         sh.out_base[s] = goff;
         sh.out_ok[s] = ok ? 1u : 0u;
-        sh.ok_ring[k & 7] = ok ? 1u : 0u;
-        sh.base_ring[k & 7] = goff;
         mbar_arrive(&sh.base_ready[s]);
         if (ok && v.lt == p.tiles_per_seg - 1 && p.size_out) p.size_out[v.g] = goff + tot;
         if (fatal_error(ws.ctrl)) *abort = 1;
       }
+      if ((uint32_t)lane == (k & 31u)) {
+        my_lt = v.lt;
+        my_g = v.g;
+        my_word = flag_pack(p.ring_epoch, ok ? goff : kFlagOffsetMask);
+      }
+      const uint32_t out = kHasIn ? k : (k >= 1 ? k - 1 : 0u);  // tiles [0, out) are stored
+      if (out - flagged >= kFlagBatch) raise_flags(out);
     }
   } else {
     // ================================ compute warps ==============================================
     for (uint32_t k = 0;; ++k) {
       const int s = k % NS, slot = k & 7;
       uint8_t* const stage_s = stage0 + s * kStagePitch;
-      bool alive = wait_or_flag(&sh.tma_full[s], (k / NS) & 1, ws, abort);
-      if (k == 0 && tid == 0) HC_STAMP(2);
-      const uint32_t tile = alive ? sh.tile[slot] : kNoTile;
-      if (tile == kNoTile) {
-        if (kLag && k >= 1) {
-          compute_barrier();  // no scan barrier this turn: wait until every thread has packed
-          move_out(k - 1);
-          if (k == 1 && tid == 0) HC_STAMP(5);
-        }
-        if (tid == 0) mbar_arrive(&sh.scan_done[s]);  // wakes the scanner, which sees the end marker too
-        break;
-      }
-      const Seg v = seg_of(tile);
       int32_t d[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) d[i] = 0;
 
       // ---- incoming stream(s) -> signed deltas, summed -------------------------------------------
+      bool end = false;
       if (kHasIn) {
         for (uint32_t q = 0; q < Q; ++q) {
           const uint32_t vv = k * Q + q, b = vv & 1u;
           const bool staged = wait_or_flag(&sh.in_full[b], (vv >> 1) & 1, ws, abort);
+          if (q == 0 && (!staged || sh.in_end[b])) {
+            end = true;  // no tile this turn (or the loader gave up)
+            break;
+          }
           const uint32_t rate_in = staged ? sh.in_rate[b][tid] : 0u;
           const uint32_t pos = sh.in_phase[b] + sh.in_rel[b][tid];
           int W = plane_width(rate_in & 31u);
@@ -440,7 +460,26 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
           mbar_arrive(&sh.in_free[b]);
           if (k == 0 && tid == 0 && q < 8) HC_STAMP(8 + q);
         }
+        if (k >= 1) {
+          compute_barrier();  // every thread has packed tile k-1
+          move_out(k - 1);
+          if (k == 1 && tid == 0) HC_STAMP(5);
+        }
       }
+      const bool alive = !end && wait_or_flag(&sh.tma_full[s], (k / NS) & 1, ws, abort);
+      if (k == 0 && tid == 0) HC_STAMP(2);
+      const uint32_t tile = alive ? sh.tile[slot] : kNoTile;
+      if (tile == kNoTile) {
+        if (!kHasIn && k >= 1) {
+          compute_barrier();  // no scan barrier this turn: wait until every thread has packed
+          move_out(k - 1);
+          if (k == 1 && tid == 0) HC_STAMP(5);
+        }
+        compute_barrier();  // every thread's stores of the last tile are issued before the scanner hears of the end
+        if (tid == 0) mbar_arrive(&sh.scan_done[s]);  // wakes the scanner, which sees the end marker too
+        break;
+      }
+      const Seg v = seg_of(tile);
 
       // ---- local operand -------------------------------------------------------------------------
       if (kHasLocal) {
@@ -500,11 +539,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       W = __reduce_max_sync(0xffffffffu, W);
       transpose_forward(A, W);
       write_payload(stage_s, rel, code, A, W);
-      if (kLag == 0) {
-        compute_barrier();  // every thread's payload is packed
-        move_out(k);
-        if (k == 0 && tid == 0) HC_STAMP(5);
-      } else if (k >= 1) {
+      if (!kHasIn && k >= 1) {
         move_out(k - 1);  // packed before this turn's scan barrier
         if (k == 1 && tid == 0) HC_STAMP(5);
       }
@@ -539,6 +574,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const Workspace& ws = p.ws;
+  HC_TL_DECL(ws.epoch);
   const float eb = p.eb;
   const uint32_t groups_per_seg = p.tiles_per_seg / 32 + 1;
 
@@ -549,15 +585,11 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
     }
     fence_mbar_init();
     sh.abort = fatal_error(ws.ctrl) ? 1u : 0u;
+    HC_TL_ZERO();
   }
   __syncthreads();
   volatile uint32_t* abort = &sh.abort;
-  if (tid == 0) {
-    HC_STAMP(0);
-#ifdef HC_TIMELINE
-    if (blockIdx.x < 4096) g_timeline[blockIdx.x * 16 + 7] = 0;
-#endif
-  }
+  if (tid == 0) HC_STAMP(0);
 
   if (warp == kComputeThreads / 32) {
     // ================================ loader warp ================================================
@@ -934,13 +966,12 @@ cudaError_t launch_sum(float* dst, const float* a, const float* b, const float* 
 }  // namespace hc
 
 #ifdef HC_TIMELINE
-// copies the stamps of the last launch to the host (synchronises) and clears them
-extern "C" int hc_debug_timeline(unsigned long long* host, int n_ctas) {
-  if (n_ctas > 4096) n_ctas = 4096;
+// copies the stamps of the last four launches (4 x 1024 CTAs x 16 slots) to the host (synchronises) and clears them
+extern "C" int hc_debug_timeline(unsigned long long* host) {
   if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-  if (cudaMemcpyFromSymbol(host, hc::dev::g_timeline, (size_t)n_ctas * 16 * sizeof(unsigned long long)) != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(host, hc::dev::g_timeline, sizeof(hc::dev::g_timeline)) != cudaSuccess) return -1;
   void* sym = nullptr;
   if (cudaGetSymbolAddress(&sym, hc::dev::g_timeline) == cudaSuccess) cudaMemset(sym, 0, sizeof(hc::dev::g_timeline));
-  return n_ctas;
+  return 0;
 }
 #endif
