@@ -115,7 +115,7 @@ int hc_codec_status(hc_codec* c, int clear) {
   uint32_t ctrl[4] = {0, 0, 0, 0};
   if (cudaDeviceSynchronize() != cudaSuccess) return hc::kErrCuda;
   if (cudaMemcpy(ctrl, c->ws_mem, sizeof(ctrl), cudaMemcpyDeviceToHost) != cudaSuccess) return hc::kErrCuda;
-  if (clear && (ctrl[2] != 0 || ctrl[0] != 0 || ctrl[1] != 0)) cudaMemset(c->ws_mem, 0, 16);
+  if (clear && (ctrl[2] != 0 || ctrl[0] != 0 || ctrl[1] != 0)) cudaMemset(c->ws_mem, 0, 64);  // status and ticket counters
   return (int)ctrl[2];
 }
 

@@ -127,6 +127,9 @@ __device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint32_t a, uint32
                "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
                : "memory");
 }
+// programmatic dependent launch: lets the runtime schedule the next kernel of the stream (if it was
+// launched with programmatic serialisation) once every CTA of this grid has got here or has left
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ uint4 ld_cg_u4(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
 __device__ __forceinline__ uint32_t ld_cg_u8(const uint8_t* p) { return (uint32_t)__ldcg(p); }

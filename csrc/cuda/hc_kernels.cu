@@ -65,14 +65,14 @@ __device__ __forceinline__ unsigned long long timeline_now() {
 #endif
 
 // the last CTA to leave re-arms the ticket counter for the next launch
-__device__ __forceinline__ void cta_epilogue(uint32_t* ctrl) {
+__device__ __forceinline__ void cta_epilogue(uint32_t* tick) {
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
-    uint32_t done = atomicAdd(ctrl + 1, 1u);
+    uint32_t done = atomicAdd(tick + 1, 1u);
     if (done == gridDim.x - 1) {
-      ctrl[0] = 0;
-      ctrl[1] = 0;
+      tick[0] = 0;
+      tick[1] = 0;
       __threadfence();
     }
   }
@@ -239,6 +239,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
     fence_mbar_init();
     sh.abort = fatal_error(ws.ctrl) ? 1u : 0u;
     HC_TL_ZERO();
+    launch_dependents();  // a following launch with programmatic serialisation may fill the SMs as CTAs leave
     sh.in_end[0] = sh.in_end[1] = 0u;
   }
   __syncthreads();
@@ -261,14 +262,16 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
   };
   if (warp == kComputeThreads / 32) {
     // ================================ loader warp ================================================
-    // Software pipeline over this CTA's tiles: the ticket is taken two turns ahead and the rate
-    // bytes of the next input tile one turn ahead, so neither round trip sits between two
-    // look-backs.  Per tile: the input streams first (their aggregates are published before any
+    // Tiles: CTA i starts with tile i (no round trip, and a CTA that starts late, behind a launch
+    // that is still draining, finds its tile waiting instead of taken by an early starter); the
+    // tiles past the grid come from a shared ticket counter.  Software pipeline over this CTA's
+    // tiles: the ticket is taken two turns ahead and the rate bytes of the next input tile one
+    // turn ahead, so neither round trip sits between two look-backs.  Per tile: the input streams first (their aggregates are published before any
     // wait on this CTA's compute warps), then the fp32 tile's TMA load once its stage is free.
     // Input stream q of this CTA's k-th tile is staging job v = k * Q + q: buffer v & 1.
     auto take = [&]() -> uint32_t {
       uint32_t t = kNoTile;
-      if (lane == 0 && !*abort) t = atomicAdd(ws.ctrl, 1u);
+      if (lane == 0 && !*abort) t = gridDim.x + atomicAdd(ws.tick, 1u);
       t = __shfl_sync(0xffffffffu, t, 0);
       return t < p.n_tiles ? t : kNoTile;
     };
@@ -280,7 +283,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       loader_fetch_rates(p.in[q], p.in_size[q], t, r);
       return true;
     };
-    uint32_t tile = take();
+    uint32_t tile = (!*abort && blockIdx.x < p.n_tiles) ? blockIdx.x : kNoTile;
     if (lane == 0) HC_STAMP(1);
     uint32_t tile_n = tile != kNoTile ? take() : kNoTile;
     uint32_t rates[kRatesPerLane] = {}, rates_n[kRatesPerLane] = {};
@@ -546,7 +549,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
     }
   }
   if (lane == 0) HC_STAMP_MAX(7);
-  cta_epilogue(ws.ctrl);
+  cta_epilogue(ws.tick);
 }
 
 struct __align__(16) DecShared {
@@ -586,6 +589,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
     fence_mbar_init();
     sh.abort = fatal_error(ws.ctrl) ? 1u : 0u;
     HC_TL_ZERO();
+    launch_dependents();  // a following launch with programmatic serialisation may fill the SMs as CTAs leave
   }
   __syncthreads();
   volatile uint32_t* abort = &sh.abort;
@@ -593,11 +597,12 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
 
   if (warp == kComputeThreads / 32) {
     // ================================ loader warp ================================================
-    // Software pipeline over this CTA's tiles: the ticket is taken two turns ahead and the rate
-    // bytes one turn ahead, so neither round trip sits between two look-backs.
+    // CTA i starts with tile i, later tiles come from the shared ticket counter.  Software pipeline
+    // over this CTA's tiles: the ticket is taken two turns ahead and the rate bytes one turn ahead,
+    // so neither round trip sits between two look-backs.
     auto take = [&]() -> uint32_t {  // lane 0 takes a ticket, every lane gets it
       uint32_t t = kNoTile;
-      if (lane == 0 && !*abort) t = atomicAdd(ws.ctrl, 1u);
+      if (lane == 0 && !*abort) t = gridDim.x + atomicAdd(ws.tick, 1u);
       t = __shfl_sync(0xffffffffu, t, 0);
       return t < p.n_tiles ? t : kNoTile;
     };
@@ -611,7 +616,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
       loader_fetch_rates(seg.in, seg.in_size, lt, r);
       return true;
     };
-    uint32_t tile = take();
+    uint32_t tile = (!*abort && blockIdx.x < p.n_tiles) ? blockIdx.x : kNoTile;
     if (lane == 0) HC_STAMP(1);
     uint32_t tile_n = tile != kNoTile ? take() : kNoTile;
     uint32_t rates[kRatesPerLane] = {}, rates_n[kRatesPerLane] = {};
@@ -708,7 +713,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
     if (tid == 0) tma_wait_group<0>();
   }
   if (lane == 0) HC_STAMP_MAX(7);
-  cta_epilogue(ws.ctrl);
+  cta_epilogue(ws.tick);
 }
 
 // fp32 -> int32 Lorenzo deltas of the quantised values, padded with zero deltas to whole blocks.
@@ -821,8 +826,27 @@ cudaError_t set_smem(K kernel, int bytes) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 
+// launch with programmatic stream serialisation (see launch_encode in hc_launch.h)
+template <typename... Params, typename... Args>
+cudaError_t launch_overlapped(void (*kernel)(Params...), int grid, int block, int smem, cudaStream_t stream,
+                              const Args&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)block);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  memset(&attr, 0, sizeof(attr));
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <int OP, int MODE>
-cudaError_t launch_encode_t(const TensorMaps& map, const EncParams& p, int grid, cudaStream_t stream) {
+cudaError_t launch_encode_t(const TensorMaps& map, const EncParams& p, int grid, cudaStream_t stream, bool overlap) {
   constexpr int smem = OP == kOpCompress ? kEncSmemLocalOnly : kEncSmemWithIn;
   static thread_local bool attr_done[64] = {};
   int dev = 0;
@@ -832,22 +856,24 @@ cudaError_t launch_encode_t(const TensorMaps& map, const EncParams& p, int grid,
     if (e != cudaSuccess) return e;
     attr_done[dev & 63] = true;
   }
+  if (overlap) return launch_overlapped(dev::hc_encode_kernel<OP, MODE>, grid, dev::kEncThreads, smem, stream, map, p);
   dev::hc_encode_kernel<OP, MODE><<<grid, dev::kEncThreads, smem, stream>>>(map, p);
   return cudaGetLastError();
 }
 
 template <int OP>
-cudaError_t launch_encode_m(int mode, const TensorMaps& map, const EncParams& p, int grid, cudaStream_t stream) {
+cudaError_t launch_encode_m(int mode, const TensorMaps& map, const EncParams& p, int grid, cudaStream_t stream,
+                            bool overlap) {
   switch (mode) {
-    case kModeOutlier: return launch_encode_t<OP, kModeOutlier>(map, p, grid, stream);
-    case kModePlain: return launch_encode_t<OP, kModePlain>(map, p, grid, stream);
-    case kModeVec: return launch_encode_t<OP, kModeVec>(map, p, grid, stream);
+    case kModeOutlier: return launch_encode_t<OP, kModeOutlier>(map, p, grid, stream, overlap);
+    case kModePlain: return launch_encode_t<OP, kModePlain>(map, p, grid, stream, overlap);
+    case kModeVec: return launch_encode_t<OP, kModeVec>(map, p, grid, stream, overlap);
     default: return cudaErrorInvalidValue;
   }
 }
 
 template <int MODE>
-cudaError_t launch_decode_t(const TensorMaps& maps, const DecParams& p, int grid, cudaStream_t stream) {
+cudaError_t launch_decode_t(const TensorMaps& maps, const DecParams& p, int grid, cudaStream_t stream, bool overlap) {
   static thread_local bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -856,6 +882,7 @@ cudaError_t launch_decode_t(const TensorMaps& maps, const DecParams& p, int grid
     if (e != cudaSuccess) return e;
     attr_done[dev & 63] = true;
   }
+  if (overlap) return launch_overlapped(dev::hc_decode_kernel<MODE>, grid, dev::kDecThreads, kDecSmem, stream, maps, p);
   dev::hc_decode_kernel<MODE><<<grid, dev::kDecThreads, kDecSmem, stream>>>(maps, p);
   return cudaGetLastError();
 }
@@ -866,19 +893,25 @@ cudaError_t launch_decode_t(const TensorMaps& maps, const DecParams& p, int grid
 static size_t workspace_tiles(size_t max_elems) {
   return rate_bytes(max_elems) / kTileBlocks + (size_t)kMaxDst * (kBlocksPerChunk / kTileBlocks) + 1;
 }
-size_t workspace_bytes(size_t max_elems) {
+size_t workspace_bytes(size_t max_elems, int sets) {
   size_t tiles = workspace_tiles(max_elems);
   size_t groups = tiles / 32 + 1 + kMaxDst;
-  return 256 + 3 * (tiles + groups) * sizeof(uint64_t);
+  if (sets < 1) sets = 1;
+  if (sets > kMaxWorkspaceSets) sets = kMaxWorkspaceSets;
+  return 256 + (size_t)sets * 3 * (tiles + groups) * sizeof(uint64_t);
 }
 
-Workspace workspace_view(void* mem, size_t max_elems, uint32_t epoch, uint64_t spin_limit_ns) {
+Workspace workspace_view(void* mem, size_t max_elems, uint32_t epoch, uint64_t spin_limit_ns, int sets) {
   size_t tiles = workspace_tiles(max_elems);
   Workspace w;
   uint8_t* b = static_cast<uint8_t*>(mem);
   w.ctrl = reinterpret_cast<uint32_t*>(b);
   size_t groups = tiles / 32 + 1 + kMaxDst;
-  w.st_a = reinterpret_cast<uint64_t*>(b + 256);
+  if (sets < 1) sets = 1;
+  if (sets > kMaxWorkspaceSets) sets = kMaxWorkspaceSets;
+  const size_t set = epoch % (uint32_t)sets;
+  w.tick = w.ctrl + 8 + 2 * set;  // words 8..15 of the header
+  w.st_a = reinterpret_cast<uint64_t*>(b + 256) + set * 3 * (tiles + groups);
   w.st_b = w.st_a + tiles;
   w.st_out = w.st_b + tiles;
   w.grp_a = w.st_out + tiles;
@@ -895,7 +928,7 @@ int grid_for_tiles(uint32_t n_tiles, int ctas_per_sm) {
   return (int)(n_tiles < (uint32_t)cap ? n_tiles : (uint32_t)cap);
 }
 
-cudaError_t launch_encode(int op, int mode, EncParams p, cudaStream_t stream) {
+cudaError_t launch_encode(int op, int mode, EncParams p, cudaStream_t stream, bool overlap) {
   if (p.n_seg == 0 || p.n_seg > (uint32_t)kMaxDst || p.n_in > (uint32_t)kMaxIn) return cudaErrorInvalidValue;
   if (p.n_seg > 1 && (op != kOpCompress || p.n_in != 0)) return cudaErrorInvalidValue;
   if (op == kOpCompress) p.n_in = 0;
@@ -916,15 +949,15 @@ cudaError_t launch_encode(int op, int mode, EncParams p, cudaStream_t stream) {
   }
   int grid = grid_for_tiles(p.n_tiles, op == kOpCompress ? 4 : 3);
   switch (op) {
-    case kOpCompress: return launch_encode_m<kOpCompress>(mode, maps, p, grid, stream);
-    case kOpAddF32: return launch_encode_m<kOpAddF32>(mode, maps, p, grid, stream);
-    case kOpAddI32: return launch_encode_m<kOpAddI32>(mode, maps, p, grid, stream);
-    case kOpAddStream: return launch_encode_m<kOpAddStream>(mode, maps, p, grid, stream);
+    case kOpCompress: return launch_encode_m<kOpCompress>(mode, maps, p, grid, stream, overlap);
+    case kOpAddF32: return launch_encode_m<kOpAddF32>(mode, maps, p, grid, stream, overlap);
+    case kOpAddI32: return launch_encode_m<kOpAddI32>(mode, maps, p, grid, stream, overlap);
+    case kOpAddStream: return launch_encode_m<kOpAddStream>(mode, maps, p, grid, stream, overlap);
     default: return cudaErrorInvalidValue;
   }
 }
 
-cudaError_t launch_decode(int mode, DecParams p, cudaStream_t stream) {
+cudaError_t launch_decode(int mode, DecParams p, cudaStream_t stream, bool overlap) {
   if (p.n_seg == 0 || p.n_seg > (uint32_t)kMaxDst) return cudaErrorInvalidValue;
   uint64_t n_max = 0;
   for (uint32_t i = 0; i < p.n_seg; ++i) n_max = p.seg[i].n > n_max ? p.seg[i].n : n_max;
@@ -938,8 +971,8 @@ cudaError_t launch_decode(int mode, DecParams p, cudaStream_t stream) {
   int grid = grid_for_tiles(p.n_tiles, 4);
   switch (mode) {
     case kModeOutlier:
-    case kModePlain: return launch_decode_t<kModeOutlier>(maps, p, grid, stream);
-    case kModeVec: return launch_decode_t<kModeVec>(maps, p, grid, stream);
+    case kModePlain: return launch_decode_t<kModeOutlier>(maps, p, grid, stream, overlap);
+    case kModeVec: return launch_decode_t<kModeVec>(maps, p, grid, stream, overlap);
     default: return cudaErrorInvalidValue;
   }
 }

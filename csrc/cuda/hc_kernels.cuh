@@ -48,13 +48,14 @@ enum Op : int {
 };
 
 struct Workspace {
-  uint32_t* ctrl;    // [0] ticket, [1] CTAs done, [2] sticky error (hc::Status), [3] spare
+  uint32_t* ctrl;    // [2] sticky error (hc::Status); the other words of the 256-byte header hold the tick sets
   uint64_t* st_a;    // look-back chain of the first input stream (tile words, then group words)
   uint64_t* st_b;    // look-back chain of the second input stream
   uint64_t* st_out;  // look-back chain of the output stream
   uint64_t* grp_a;
   uint64_t* grp_b;
   uint64_t* grp_out;
+  uint32_t* tick;  // [0] tile ticket counter, [1] CTAs that have left; re-armed by the last CTA of a launch
   uint32_t epoch;
   uint64_t spin_limit_ns;
 };

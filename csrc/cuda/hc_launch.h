@@ -9,12 +9,18 @@ namespace hc {
 
 // Bytes of device workspace for calls of up to max_elems values.  The workspace must be zeroed
 // once when it is created; launches never clear it again.
-size_t workspace_bytes(size_t max_elems);
-Workspace workspace_view(void* mem, size_t max_elems, uint32_t epoch, uint64_t spin_limit_ns);
+// `sets` > 1 gives consecutive launches (epoch % sets) their own look-back words and ticket counters,
+// so that a launch may start while its predecessor on the stream is still draining.
+constexpr int kMaxWorkspaceSets = 4;
+size_t workspace_bytes(size_t max_elems, int sets = 1);
+Workspace workspace_view(void* mem, size_t max_elems, uint32_t epoch, uint64_t spin_limit_ns, int sets = 1);
 int grid_for_tiles(uint32_t n_tiles, int ctas_per_sm);
 
-cudaError_t launch_encode(int op, int mode, EncParams p, cudaStream_t stream);
-cudaError_t launch_decode(int mode, DecParams p, cudaStream_t stream);
+// `overlap`: programmatic dependent launch: the kernel may start as soon as every CTA of the previous
+// kernel on the stream is running, and fills the SMs as that kernel's CTAs leave.  Only for launches
+// whose inputs are ordered by arrival flags, with a workspace view of their own set.
+cudaError_t launch_encode(int op, int mode, EncParams p, cudaStream_t stream, bool overlap = false);
+cudaError_t launch_decode(int mode, DecParams p, cudaStream_t stream, bool overlap = false);
 cudaError_t launch_quant_pred(int mode, const float* x, int32_t* deltas, uint64_t n, float eb, cudaStream_t stream);
 cudaError_t launch_sum(float* dst, const float* a, const float* b, const float* c, const float* d, uint64_t n,
                        cudaStream_t stream);

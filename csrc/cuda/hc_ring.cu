@@ -74,6 +74,7 @@ struct hc_comm {
   uint32_t raw_call = 0;
   int algorithm = 1;              // 0 ring (P + 1 kernels), 1 direct (3 kernels)
   bool trace = false;             // record one CUDA event per step of hc_allreduce
+  bool overlap = true;            // direct algorithm: steps 2 and 3 start while their predecessor drains
   cudaEvent_t ev[hc::kMaxDst + 3] = {};
   int n_ev = 0;
   uint64_t spin_limit_ns = 2000ull * 1000 * 1000;
@@ -87,7 +88,7 @@ hc::Workspace next_ws(hc_comm* c, cudaStream_t stream) {
     cudaMemsetAsync(static_cast<uint8_t*>(c->ws_mem) + 256, 0, c->ws_bytes - 256, stream);
     c->ws_epoch = 1;
   }
-  return hc::workspace_view(c->ws_mem, c->max_count, c->ws_epoch, c->spin_limit_ns);
+  return hc::workspace_view(c->ws_mem, c->max_count, c->ws_epoch, c->spin_limit_ns, hc::kMaxWorkspaceSets);
 }
 
 }  // namespace
@@ -115,7 +116,7 @@ int hc_comm_create(hc_comm** out, int rank, int world, size_t max_count, void* c
     c->peer.push_back(static_cast<uint8_t*>(peer_bases[r]));
   }
   c->mc = static_cast<uint8_t*>(mc_base);
-  c->ws_bytes = hc::workspace_bytes(max_count);
+  c->ws_bytes = hc::workspace_bytes(max_count, hc::kMaxWorkspaceSets);
   if (cudaMalloc(&c->ws_mem, c->ws_bytes) != cudaSuccess || cudaMemset(c->ws_mem, 0, c->ws_bytes) != cudaSuccess ||
       cudaMalloc(&c->sizes, 16 * sizeof(uint64_t)) != cudaSuccess ||
       cudaMemset(c->sizes, 0, 16 * sizeof(uint64_t)) != cudaSuccess) {
@@ -168,7 +169,7 @@ int hc_comm_status(hc_comm* c, int clear) {
   uint32_t ctrl[4] = {0, 0, 0, 0};
   if (cudaDeviceSynchronize() != cudaSuccess) return hc::kErrCuda;
   if (cudaMemcpy(ctrl, c->ws_mem, sizeof(ctrl), cudaMemcpyDeviceToHost) != cudaSuccess) return hc::kErrCuda;
-  if (clear && (ctrl[0] | ctrl[1] | ctrl[2])) cudaMemset(c->ws_mem, 0, 16);
+  if (clear && (ctrl[0] | ctrl[1] | ctrl[2])) cudaMemset(c->ws_mem, 0, 64);  // status and ticket counters
   return (int)ctrl[2];
 }
 
@@ -301,6 +302,12 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
   auto mark = [&]() {
     if (c->trace) cudaEventRecord(c->ev[c->n_ev++], stream);
   };
+  // Steps 2 and 3 only consume what arrival flags announce and use a workspace set of their own, so
+  // they may start while the step before them drains (never across calls: step 1 of the next call
+  // waits for this call to end, which the reuse of slots and flags relies on).  An event between two
+  // launches would undo the overlap, hence not while tracing.
+  const bool overlap = c->overlap && !c->trace;
+  bool launched = false;  // a kernel of this call is already on the stream
   mark();
   // ---- 1. scatter: chunk d -> rank d's slot for source r ------------------------------------------
   if (P > 1) {
@@ -325,6 +332,7 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
       p.n_dst = 1;
       p.ws = next_ws(c, stream);
       if (hc::launch_encode(hc::kOpCompress, hc::kModeOutlier, p, stream) != cudaSuccess) return hc::kErrCuda;
+      launched = true;
     }
   }
   mark();
@@ -355,8 +363,10 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
     }
     if (c->mc && P > 1) p.out_mc = c->mc + L.data_off(slot);  // one multimem store reaches all P copies
     p.ws = next_ws(c, stream);
-    if (hc::launch_encode(P > 1 ? hc::kOpAddF32 : hc::kOpCompress, hc::kModeOutlier, p, stream) != cudaSuccess)
+    if (hc::launch_encode(P > 1 ? hc::kOpAddF32 : hc::kOpCompress, hc::kModeOutlier, p, stream, overlap && launched) !=
+        cudaSuccess)
       return hc::kErrCuda;
+    launched = true;
   }
   mark();
   // ---- 3. decode the P reduced chunks as their tiles arrive ----------------------------------------
@@ -377,7 +387,7 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
     sg.n = n;
   }
   d.ws = next_ws(c, stream);
-  if (hc::launch_decode(hc::kModeOutlier, d, stream) != cudaSuccess) return hc::kErrCuda;
+  if (hc::launch_decode(hc::kModeOutlier, d, stream, overlap && launched) != cudaSuccess) return hc::kErrCuda;
   mark();
   return hc::kOk;
 }
@@ -385,6 +395,12 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
 extern "C" int hc_comm_set_algorithm(hc_comm* c, int algorithm) {
   if (!c || algorithm < 0 || algorithm > 1) return hc::kErrArgument;
   c->algorithm = algorithm;
+  return hc::kOk;
+}
+
+extern "C" int hc_comm_set_overlap(hc_comm* c, int on) {
+  if (!c) return hc::kErrArgument;
+  c->overlap = on != 0;
   return hc::kOk;
 }
 

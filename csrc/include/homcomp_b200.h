@@ -124,6 +124,9 @@ int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, f
 // algorithm 1 (default): direct scatter -> reduce -> gather for a switched fabric (3 launches).
 // Both produce byte-identical reduced streams, hence bit-identical results.
 int hc_comm_set_algorithm(hc_comm* c, int algorithm);
+// Direct algorithm: launch steps 2 and 3 with programmatic stream serialisation, so that each fills
+// the SMs while its predecessor drains (default on; off while tracing).  Same results either way.
+int hc_comm_set_overlap(hc_comm* c, int on);
 // Uncompressed sum over the same peer mappings (two-shot direct algorithm, three kernels); the
 // compressed and the uncompressed collective of one handle must not be in flight together.
 int hc_allreduce_raw(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, hc_stream_t stream);

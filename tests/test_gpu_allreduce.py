@@ -28,9 +28,12 @@ def _worker(rank, world, counts, eb, algorithm="direct"):
         np.testing.assert_array_equal(got, want)
         exact = np.sum(np.stack(bufs).astype(np.float64), axis=0)
         assert np.abs(got - exact).max() <= world * eb * 1.01 + 1e-6
-        # in place, and again (flags and slots are reused without any reset)
+        # in place, and again (flags and slots are reused without any reset); with the steps of the
+        # direct algorithm strictly one after the other this time
         y = x.clone()
+        ar.set_overlap(False)
         ar.allreduce(y, None, eb)
+        ar.set_overlap(True)
         np.testing.assert_array_equal(y.cpu().numpy(), want)
     sizes = ar.last_stream_bytes()
     assert all(s > 0 for s in sizes)

@@ -20,6 +20,7 @@ def declare(lib):
         "hc_allreduce_raw": [vp, vp, vp, sz, vp],
         "hc_comm_set_trace": [vp, i],
         "hc_comm_set_algorithm": [vp, i],
+        "hc_comm_set_overlap": [vp, i],
         "hc_comm_last_step_ms": [vp, C.POINTER(C.c_float), i],
         "hc_comm_last_stream_bytes": [vp, C.POINTER(C.c_uint64), i],
         "hc_ipc_alloc": [C.POINTER(vp), sz, C.c_char_p],

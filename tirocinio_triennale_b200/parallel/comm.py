@@ -125,6 +125,11 @@ class CompressedAllreduce:
         _lib.check(self.lib.hc_comm_set_algorithm(self._h, code), "set_algorithm")
         self.algorithm = algorithm
 
+    def set_overlap(self, on: bool = True):
+        """Direct algorithm: let steps 2 and 3 start while their predecessor drains (programmatic
+        dependent launch; default on, ignored while tracing).  Results do not depend on it."""
+        _lib.check(self.lib.hc_comm_set_overlap(self._h, 1 if on else 0), "set_overlap")
+
     def set_trace(self, on: bool = True):
         """Record one CUDA event per step of every following allreduce (see ``last_step_ms``)."""
         _lib.check(self.lib.hc_comm_set_trace(self._h, 1 if on else 0), "set_trace")
