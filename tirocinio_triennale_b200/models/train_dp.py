@@ -7,6 +7,11 @@ Runs the same seeded training twice: fp32 gradient buckets of 25 MB averaged (a)
 library's compressed allreduce through the DDP communication hook, overlapped with backward on a
 side stream, and (b) with plain NCCL.  Prints one JSON line with tokens/s of both runs and the loss
 gap after the last step.  Random-init weights, uniform random token ids (no dataset, no download).
+
+``--save PATH`` writes model, optimiser, step count and the data generator's state after the last
+step (rank 0; one file per arm: PATH.compressed / PATH.nccl); ``--resume PATH`` continues from such
+files, bit for bit the run that was never interrupted.  ``--save-compressed-eb EB`` additionally
+writes the model weights as error-bounded streams (PATH.*.hcz, ``ops.stream_io.save_state``).
 """
 from __future__ import annotations
 
@@ -36,6 +41,14 @@ def run(args, compressed: bool, rank: int, world: int, device):
         ddp.register_comm_hook(state, compressed_allreduce_hook)
     opt = torch.optim.AdamW(ddp.parameters(), lr=args.lr, weight_decay=0.0, fused=device.type == "cuda")
     g = torch.Generator(device="cpu").manual_seed(100 + rank)
+    arm = "compressed" if compressed else "nccl"
+    start = 0
+    if getattr(args, "resume", None):
+        ck = torch.load("%s.%s.rank%d" % (args.resume, arm, rank), map_location=device, weights_only=False)
+        model.load_state_dict(ck["model"])
+        opt.load_state_dict(ck["opt"])
+        g.set_state(ck["gen"])
+        start = int(ck["step"])
     losses = []
     t0 = None
     for step in range(args.steps + args.warmup):
@@ -58,7 +71,16 @@ def run(args, compressed: bool, rank: int, world: int, device):
     last = torch.stack(losses[-5:]).float().mean()
     dist.all_reduce(last)
     out = {"tokens_per_s": args.steps * args.batch * args.seq * world / dt, "final_loss": float(last) / world,
-           "first_loss": float(losses[0])}
+           "first_loss": float(losses[0]), "last_loss_rank0": float(losses[-1]), "steps_done": start + len(losses)}
+    if getattr(args, "save", None):
+        # every rank keeps its own data generator state; the weights are identical on all ranks
+        torch.save({"model": model.state_dict(), "opt": opt.state_dict(), "gen": g.get_state(),
+                    "step": start + len(losses)}, "%s.%s.rank%d" % (args.save, arm, rank))
+        if rank == 0 and getattr(args, "save_compressed_eb", 0.0):
+            from ..ops import stream_io
+
+            out["compressed_checkpoint"] = stream_io.save_state("%s.%s.hcz" % (args.save, arm), model.state_dict(),
+                                                                args.save_compressed_eb)
     if state is not None:
         out["hook_calls"] = state.calls
         out["compressed_calls"] = state.compressed_calls
@@ -78,6 +100,10 @@ def main(argv=None):
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--bucket-mb", type=float, default=25.0)
     ap.add_argument("--cpu", action="store_true", help="gloo + host-rank ring (functional check without GPUs)")
+    ap.add_argument("--save", default=None, help="checkpoint prefix written after the last step")
+    ap.add_argument("--resume", default=None, help="checkpoint prefix to continue from")
+    ap.add_argument("--save-compressed-eb", type=float, default=0.0,
+                    help="also write the weights as error-bounded streams with this absolute bound")
     args = ap.parse_args(argv)
 
     rank = int(os.environ.get("RANK", "0"))
@@ -101,6 +127,7 @@ def main(argv=None):
                               "compressed": a, "nccl": b,
                               "loss_gap": a["final_loss"] - b["final_loss"],
                               "speedup_vs_nccl": a["tokens_per_s"] / b["tokens_per_s"]}), flush=True)
+        return {"compressed": a, "nccl": b}
     finally:
         dist.destroy_process_group()
 

@@ -4,3 +4,4 @@ from .cpu_codec import (  # noqa: F401
     rate_bytes, chunk_elems,
 )
 from .codec import Codec  # noqa: F401
+from . import stream_io  # noqa: F401
