@@ -18,6 +18,8 @@
 //                   byte offset of the tile's payload, so consumers never re-derive offsets
 // Flags carry the call number, so nothing is ever reset; all-gather buffers alternate between two
 // sets because a fast rank may start pushing call n+1 while a slow one still decodes call n.
+#include <nvtx3/nvToolsExt.h>
+
 #include <new>
 #include <vector>
 
@@ -81,6 +83,15 @@ struct hc_comm {
 };
 
 namespace {
+
+// NVTX range on the host thread: shows where each step of a collective is enqueued in a timeline
+// tool; a no-op when no tool is attached
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+  NvtxRange(const NvtxRange&) = delete;
+  NvtxRange& operator=(const NvtxRange&) = delete;
+};
 
 hc::Workspace next_ws(hc_comm* c, cudaStream_t stream) {
   c->ws_epoch = (c->ws_epoch + 1) & hc::dev::kEpochMask;
@@ -208,6 +219,7 @@ static int allreduce_ring(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t
     const int ch = ((r - s) % P + P) % P;
     const size_t n = chunk_len(ch);
     if (n == 0) continue;
+    NvtxRange step_range(s == 0 ? "hc ring: compress" : (s < P - 1 ? "hc ring: hop" : "hc ring: last hop + all-gather"));
     hc::EncParams p;
     memset(&p, 0, sizeof(p));
     p.n_seg = 1;
@@ -247,6 +259,7 @@ static int allreduce_ring(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t
   }
 
   // ---- all-gather side: one kernel decodes the P reduced chunks as their tiles arrive ------------
+  NvtxRange decode_range("hc ring: decode");
   hc::DecParams d;
   memset(&d, 0, sizeof(d));
   d.eb = eb;
@@ -311,6 +324,7 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
   mark();
   // ---- 1. scatter: chunk d -> rank d's slot for source r ------------------------------------------
   if (P > 1) {
+    NvtxRange step_range("hc direct: scatter-compress");
     hc::EncParams p;
     memset(&p, 0, sizeof(p));
     p.recip = 0.5f / eb;
@@ -338,6 +352,7 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
   mark();
   // ---- 2. reduce the own chunk and push the result to everybody -----------------------------------
   if (const size_t n = chunk_len(r)) {
+    NvtxRange step_range("hc direct: reduce + all-gather");
     hc::EncParams p;
     memset(&p, 0, sizeof(p));
     p.n_seg = 1;
@@ -370,6 +385,7 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
   }
   mark();
   // ---- 3. decode the P reduced chunks as their tiles arrive ----------------------------------------
+  NvtxRange decode_range("hc direct: decode");
   hc::DecParams d;
   memset(&d, 0, sizeof(d));
   d.eb = eb;
@@ -407,6 +423,7 @@ extern "C" int hc_comm_set_overlap(hc_comm* c, int on) {
 extern "C" int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, float eb, hc_stream_t stream) {
   if (!c || !d_sbuf || !d_rbuf || !(eb > 0.0f) || count > c->max_count) return hc::kErrArgument;
   if (count == 0) return hc::kOk;
+  NvtxRange call_range("hc_allreduce");
   return c->algorithm == 0 ? allreduce_ring(c, d_sbuf, d_rbuf, count, eb, stream)
                            : allreduce_direct(c, d_sbuf, d_rbuf, count, eb, stream);
 }
