@@ -127,6 +127,24 @@ __device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint32_t a, uint32
                "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
                : "memory");
 }
+// Sum over every GPU bound to the multicast object, formed inside NVSwitch: one 16-byte load returns
+// the element-wise fp32 sum of the same 16 bytes of all bound memories.
+__device__ __forceinline__ float4 multimem_ld_reduce_add_v4(const void* mc_addr) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ float multimem_ld_reduce_add_f32(const void* mc_addr) {
+  float v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.f32 %0, [%1];" : "=f"(v) : "l"(mc_addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_f32(void* mc_addr, float v) {
+  asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc_addr), "f"(v) : "memory");
+}
 // programmatic dependent launch: lets the runtime schedule the next kernel of the stream (if it was
 // launched with programmatic serialisation) once every CTA of this grid has got here or has left
 __device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

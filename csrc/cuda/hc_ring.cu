@@ -433,7 +433,8 @@ extern "C" {
 // ---- uncompressed allreduce over the same peer mappings ------------------------------------------
 // Two-shot direct algorithm for NVSwitch: every rank stages its input in its symmetric region,
 // rank r sums chunk r over all ranks (peer loads, fixed rank order, so the result is bit-identical
-// everywhere) and stores it into every rank's result area (peer stores).  Takes the place of the
+// everywhere) and stores it into every rank's result area (peer stores).  With a multicast mapping
+// the sum is formed inside the switch instead (multimem.ld_reduce) and replicated by it (multimem.st).  Takes the place of the
 // reference's Open-MPI-style uncompressed ring (allreduce_ring_gpu,
 // HomComp/src/cuda_awareallreduce.cu:895-1038) and of the raw intra-node phases of its hierarchical
 // allreduce (:588-671).
@@ -447,6 +448,7 @@ struct RawParams {
   int rank, world;
   uint32_t call;
   uint8_t* peer[hc::kMaxDst];
+  uint8_t* mc;                    // multicast alias of the regions (NVLS), or null
   uint64_t s_off, r_off;          // byte offsets of the staging / result areas in a region
   uint64_t flag_off[3];           // staged, reduced, done rows
   uint32_t* ctrl;                 // [1] CTA exit counter, [2] status
@@ -503,7 +505,22 @@ __global__ void __launch_bounds__(256) hc_raw_reduce_kernel(const RawParams p) {
   __syncthreads();
   const uint64_t lo = (uint64_t)p.rank * p.chunk;
   const uint64_t hi = lo + p.chunk < p.count ? lo + p.chunk : p.count;
-  if (ok && lo < hi) {
+  if (ok && lo < hi && p.mc != nullptr) {
+    // NVLS: the switch adds the P staged copies on the way in (one multimem load per 16 bytes) and
+    // replicates the result on the way out (one multimem store); the order of the additions is the
+    // switch's, the stored bits are the same on every rank
+    const uint64_t n = hi - lo, n4 = n / 4;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, i0 = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint8_t* S = p.mc + p.s_off + lo * sizeof(float);
+    uint8_t* R = p.mc + p.r_off + lo * sizeof(float);
+    for (uint64_t i = i0; i < n4; i += stride) {
+      const float4 acc = hc::dev::multimem_ld_reduce_add_v4(S + 16 * i);
+      hc::dev::multimem_st_v4(R + 16 * i, __float_as_uint(acc.x), __float_as_uint(acc.y), __float_as_uint(acc.z),
+                              __float_as_uint(acc.w));
+    }
+    for (uint64_t i = n4 * 4 + i0; i < n; i += stride)
+      hc::dev::multimem_st_f32(R + 4 * i, hc::dev::multimem_ld_reduce_add_f32(S + 4 * i));
+  } else if (ok && lo < hi) {
     const uint64_t n = hi - lo, n4 = n / 4;  // chunk starts are multiples of 32 floats
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, i0 = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     for (uint64_t i = i0; i < n4; i += stride) {
@@ -563,6 +580,7 @@ extern "C" int hc_allreduce_raw(hc_comm* c, const float* d_sbuf, float* d_rbuf, 
   p.world = c->world;
   p.call = c->raw_call;
   for (int r = 0; r < c->world; ++r) p.peer[r] = c->peer[r];
+  p.mc = c->world > 1 ? c->mc : nullptr;
   p.s_off = 0;
   p.r_off = (uint64_t)L.raw_capacity_floats() * sizeof(float);
   for (int k = 0; k < 3; ++k) p.flag_off[k] = L.raw_flag(k, 0);

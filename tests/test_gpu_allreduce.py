@@ -37,6 +37,9 @@ def _worker(rank, world, counts, eb, algorithm="direct"):
         np.testing.assert_array_equal(y.cpu().numpy(), want)
     sizes = ar.last_stream_bytes()
     assert all(s > 0 for s in sizes)
+    st = ar.stats()
+    assert st["status"] == 0 and st["count"] == counts[-1] and st["stream_bytes"] == sizes
+    assert st["compression_ratio"] > 1.0 and st["algorithm"] == algorithm
     dist.barrier()
     ar.close()
 
@@ -111,6 +114,21 @@ def _nvls_worker(rank, world, counts, eb, note_path):
                 want = ops.cpu_ring_allreduce(bufs, eb)[rank]
                 if status != 0 or not np.array_equal(out.cpu().numpy(), want):
                     problems.append((algorithm, n, rep, status))
+    # uncompressed sum: formed inside the switch when there is a multicast mapping (its own order of
+    # additions, the same bits on every rank), by peer loads in rank order otherwise
+    n = 300_003
+    bufs = [gradient_like(n, seed=r) for r in range(world)]
+    x = torch.from_numpy(bufs[rank]).cuda()
+    for rep in range(3):
+        out = torch.zeros_like(x)
+        ar.allreduce_raw(x, out)
+        status = ar.status()
+        exact = np.sum(np.stack(bufs).astype(np.float64), axis=0)
+        err = np.abs(out.cpu().numpy().astype(np.float64) - exact).max()
+        everyone = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(everyone, out)
+        if status != 0 or err > 1e-5 or not all(torch.equal(e, out) for e in everyone):
+            problems.append(("raw", rep, status, float(err)))
     multicast = ar.multicast
     dist.barrier()
     ar.close()

@@ -101,6 +101,7 @@ class CompressedAllreduce:
         with torch.cuda.device(self.device):
             _lib.check(self.lib.hc_allreduce(self._h, send.data_ptr(), recv.data_ptr(), n, eb,
                                              torch.cuda.current_stream().cuda_stream), "allreduce")
+        self._last = (n, eb)
         return recv
 
     def allreduce_raw(self, send: torch.Tensor, recv: torch.Tensor | None = None) -> torch.Tensor:
@@ -147,6 +148,21 @@ class CompressedAllreduce:
         with torch.cuda.device(self.device):
             _lib.check(self.lib.hc_comm_last_stream_bytes(self._h, arr, 16), "last_stream_bytes")
         return list(arr)[: self.world]
+
+    def stats(self, clear_status: bool = False) -> dict:
+        """Counters of the last ``allreduce`` call (synchronises the device): bytes of every stream
+        this rank produced, compression ratio of its chunks, device time per step when tracing is
+        on, and the sticky device status."""
+        n, eb = getattr(self, "_last", (0, 0.0))
+        sizes = self.last_stream_bytes() if n else []
+        produced = [s for s in sizes if s > 0]
+        chunk_bytes = 4.0 * n / self.world
+        return {
+            "world": self.world, "rank": self.rank, "algorithm": self.algorithm, "transport": self.transport,
+            "multicast": self.multicast, "count": n, "error_bound": eb, "stream_bytes": sizes,
+            "compression_ratio": (chunk_bytes * len(produced) / sum(produced)) if produced else None,
+            "step_ms": self.last_step_ms(), "status": self.status(clear=clear_status),
+        }
 
     def close(self):
         if self._h is None:
