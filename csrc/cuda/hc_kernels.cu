@@ -179,22 +179,23 @@ __device__ __forceinline__ uint64_t flag_wait_warp(const uint64_t* flag, uint32_
 // A stage first receives the fp32 tile from the TMA unit; once every compute thread holds its row
 // in registers the same bytes become the packing buffer of the tile's payload, which leaves
 // moves out before the loader refills the stage.  NS = 3 when nothing else needs shared memory
-// (compress: 4 CTAs per SM), 2 when an input stream is staged too (3 CTAs per SM).
+// (compress: 4 CTAs per SM), 2 when an input stream is staged too (3 CTAs per SM), and 1 in the
+// variant for launches with about one tile per CTA, where a fourth CTA per SM is worth more than
+// overlap between a CTA's own tiles (the reduce step of a collective over many ranks).
 constexpr int kStagePitch = kTileBytes + 1024;
 __host__ __device__ constexpr int enc_stages(int op) { return op == kOpCompress ? 3 : 2; }
-__host__ __device__ constexpr int enc_smem_base(int op) { return 1024 + enc_stages(op) * kStagePitch; }
+__host__ __device__ constexpr int enc_smem_base(int ns) { return 1024 + ns * kStagePitch; }
 
-template <int OP, int MODE>
-__global__ void __launch_bounds__(kEncThreads, OP == kOpCompress ? 4 : 3)
+template <int OP, int MODE, int NS>
+__global__ void __launch_bounds__(kEncThreads, (OP == kOpCompress || NS == 1) ? 4 : 3)
 hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ EncShared sh;
   constexpr bool kHasLocal = OP != kOpAddStream;
   constexpr bool kHasIn = OP != kOpCompress;
-  constexpr int NS = enc_stages(OP);
   uint8_t* const stage0 = smem + 1024;
-  uint8_t* cbuf[2] = {smem + enc_smem_base(OP), smem + enc_smem_base(OP) + kBufBytes};
+  uint8_t* cbuf[2] = {smem + enc_smem_base(NS), smem + enc_smem_base(NS) + kBufBytes};
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -356,13 +357,16 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       // warps free while decoding THIS tile's first streams.
       uint32_t t_stage = kNoTile;
       const bool early = k < (uint32_t)NS;
+      // With a single stage the hand-over waits for the previous tile to leave, which the compute
+      // warps only do after decoding ALL of this tile's streams: every stream goes in first then.
+      const uint32_t before = (NS == 1 && !early) ? Q : 2u;
       if (early) t_stage = hand_over();
       if (kHasIn && tile != kNoTile)
-        for (uint32_t q = 0; q < Q && q < 2; ++q) stage_job(q);
+        for (uint32_t q = 0; q < Q && q < before; ++q) stage_job(q);
       if (!early) t_stage = hand_over();
       if (t_stage == kNoTile) break;
       if (kHasIn)
-        for (uint32_t q = 2; q < Q; ++q) stage_job(q);
+        for (uint32_t q = before; q < Q; ++q) stage_job(q);
       tile = tile_n;
       tile_n = tile_nn;
     }
@@ -817,8 +821,7 @@ DeviceInfo& device_info() {
   return d;
 }
 
-constexpr int kEncSmemLocalOnly = dev::enc_smem_base(kOpCompress) + 1024;
-constexpr int kEncSmemWithIn = dev::enc_smem_base(kOpAddF32) + 2 * kBufBytes + 1024;
+constexpr int enc_smem_bytes(int op, int ns) { return dev::enc_smem_base(ns) + (op == kOpCompress ? 0 : 2 * kBufBytes) + 1024; }
 constexpr int kDecSmem = kTileBytes + 2 * kBufBytes + 1024;
 
 template <typename K>
@@ -845,19 +848,19 @@ cudaError_t launch_overlapped(void (*kernel)(Params...), int grid, int block, in
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
-template <int OP, int MODE>
+template <int OP, int MODE, int NS = dev::enc_stages(OP)>
 cudaError_t launch_encode_t(const TensorMaps& map, const EncParams& p, int grid, cudaStream_t stream, bool overlap) {
-  constexpr int smem = OP == kOpCompress ? kEncSmemLocalOnly : kEncSmemWithIn;
+  constexpr int smem = enc_smem_bytes(OP, NS);
   static thread_local bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
-    cudaError_t e = set_smem(dev::hc_encode_kernel<OP, MODE>, smem);
+    cudaError_t e = set_smem(dev::hc_encode_kernel<OP, MODE, NS>, smem);
     if (e != cudaSuccess) return e;
     attr_done[dev & 63] = true;
   }
-  if (overlap) return launch_overlapped(dev::hc_encode_kernel<OP, MODE>, grid, dev::kEncThreads, smem, stream, map, p);
-  dev::hc_encode_kernel<OP, MODE><<<grid, dev::kEncThreads, smem, stream>>>(map, p);
+  if (overlap) return launch_overlapped(dev::hc_encode_kernel<OP, MODE, NS>, grid, dev::kEncThreads, smem, stream, map, p);
+  dev::hc_encode_kernel<OP, MODE, NS><<<grid, dev::kEncThreads, smem, stream>>>(map, p);
   return cudaGetLastError();
 }
 
@@ -948,6 +951,13 @@ cudaError_t launch_encode(int op, int mode, EncParams p, cudaStream_t stream, bo
     }
   }
   int grid = grid_for_tiles(p.n_tiles, op == kOpCompress ? 4 : 3);
+  if (op == kOpAddF32 && mode == kModeOutlier) {
+    // a fourth CTA per SM when that saves a whole round of tiles (tiles per CTA, rounded up)
+    const int grid4 = grid_for_tiles(p.n_tiles, 4);
+    const uint32_t rounds3 = (p.n_tiles + grid - 1) / grid, rounds4 = (p.n_tiles + grid4 - 1) / grid4;
+    if (rounds4 < rounds3 && rounds4 <= 2)
+      return launch_encode_t<kOpAddF32, kModeOutlier, 1>(maps, p, grid4, stream, overlap);
+  }
   switch (op) {
     case kOpCompress: return launch_encode_m<kOpCompress>(mode, maps, p, grid, stream, overlap);
     case kOpAddF32: return launch_encode_m<kOpAddF32>(mode, maps, p, grid, stream, overlap);

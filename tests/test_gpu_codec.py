@@ -171,3 +171,22 @@ def test_multi_stream_add_matches_oracle(k, n):
     out, size = codec.hom_add_multi(gs, _gpu(y), eb, stream_bytes=[s.size for s in streams])
     assert codec.status() == 0
     np.testing.assert_array_equal(_stream(out, size), want)
+
+
+@pytest.mark.parametrize("k,n", [(1, 500 * 4096 + 77), (3, 520 * 4096), (7, 1000 * 4096 + 5)])
+def test_multi_stream_add_about_one_tile_per_cta(k, n):
+    """Tile counts for which the launcher picks the single-stage, four-CTAs-per-SM variant of the
+    add kernel (one round of tiles fewer than with three CTAs per SM)."""
+    eb = 1e-4
+    codec = ops.Codec(max_elems=8 * n)
+    xs = [ALL["gradient"](n, seed=20 + i) for i in range(k)]
+    y = ALL["gradient"](n, seed=98)
+    streams = [ops.cpu_compress(x, eb) for x in xs]
+    want = ops.cpu_compress(y, eb)
+    for s in streams:
+        want = ops.cpu_hom_add_streams(want, s, n)
+    gs = [_gpu(np.concatenate([s, np.zeros(32, np.uint8)])) for s in streams]
+    for _ in range(2):
+        out, size = codec.hom_add_multi(gs, _gpu(y), eb, stream_bytes=[s.size for s in streams])
+        assert codec.status() == 0
+        np.testing.assert_array_equal(_stream(out, size), want)
