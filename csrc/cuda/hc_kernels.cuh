@@ -5,24 +5,29 @@
 // Geometry.  A tile is 128 consecutive 32-element blocks (4096 values, 16 KB of fp32).  A CTA has
 // four COMPUTE warps in which thread t owns block t of the tile, i.e. one thread per block with
 // the whole block in registers, plus a LOADER warp and a SCANNER warp:
-//   loader   takes tile tickets two turns ahead, issues the 2-D TMA tiled load of the fp32 tile
-//            ({32, 128} box, 128-byte swizzle, 3 stages for compress, 2 for the adds); for the
-//            homomorphic adds it also reads the rate bytes of every input stream's tile one turn
-//            ahead, scans them, runs the look-back of the INPUT stream and brings the tile's
-//            payload bytes into shared memory with one bulk copy (up to 8 streams per tile through
-//            two staging buffers); when the launch is a step of a collective it raises the
-//            consumers' arrival flags, one system-scope fence per four stored tiles;
-//   compute  decodes the staged payloads to deltas and sums them, quantises the local values,
-//            adds, chooses the block mode, transposes the magnitudes to bit planes in registers
-//            (hc_bitplane.h), packs the tile's payload into the stage the fp32 tile came in, and
-//            moves it to its byte offset in global or peer memory with 16-byte stores;
+//   loader   starts with tile blockIdx.x and takes further tiles from a ticket counter two turns
+//            ahead, issues the 2-D TMA tiled load of the fp32 tile ({32, 128} box, 128-byte
+//            swizzle; 3 stages for compress, 2 for the adds, 1 in the add variant that runs four
+//            CTAs per SM); for the homomorphic adds it also reads the rate bytes of every input
+//            stream's tile one turn ahead, scans them, learns the payload offset (from the tile's
+//            arrival flag in a collective step, from a look-back over the INPUT stream otherwise)
+//            and brings the payload bytes into shared memory with one bulk copy (up to 8 streams
+//            per tile through two staging buffers);
+//   compute  decodes the staged payloads to deltas and sums them, moves the PREVIOUS tile's packed
+//            payload to its byte offset in global or peer memory (16-byte stores, or one multimem
+//            store for all ranks), then quantises the local values, adds, chooses the block mode,
+//            transposes the magnitudes to bit planes in registers (hc_bitplane.h) and packs the
+//            tile's payload into the stage the fp32 tile came in;
 //   scanner  runs the two-level decoupled look-back of the OUTPUT stream as soon as the tile total
-//            is known and hands the compute warps the tile's global offset.
+//            is known and hands the compute warps the tile's global offset; when the launch is a
+//            step of a collective it raises the consumers' arrival flags (call number and payload
+//            offset in one 64-bit word), one system-scope fence per four stored tiles.
 // The roles hand tiles to each other through mbarriers, so the compute warps never wait on a
 // global-memory round trip of their own.  Look-back status words are 64-bit and epoch-tagged:
 // the workspace is never cleared between launches, and the exact stream size lands in device
-// memory (no host round trip).  Tiles are handed out by an atomic ticket, which makes the
-// look-back safe under any CTA scheduling.
+// memory (no host round trip).  The grid never exceeds what the GPU holds at once, so every tile's
+// predecessors are in the hands of CTAs that run or have finished, whatever the scheduling order;
+// every wait is bounded all the same.
 //
 // The reference runs one warp per CTA, one thread per 32 blocks with a 4 KB local-memory array per
 // thread, and needs a 4-byte device-to-host copy after every launch
