@@ -4,8 +4,8 @@
 differ in the reference only in host orchestration: two kernels or one fused kernel per hop, even
 or uneven chunks, scratch allocated per call or once.  This library has one code path that is
 fused, handles any count, and never allocates, so the five names are the same call.
-``cpuCopy_*`` (HomComp/include/nca_allreduce.cuh:3-15) are the host-staged variants: device to
-host, host-rank ring over the host network, host to device.  ``mixed_compressed_allreduce`` is
+``cpuCopy_*`` (HomComp/include/nca_allreduce.cuh:3-15) are the host-staged variants: the device
+codec does the work, every compressed chunk crosses the host (pinned bounce buffer, host network).  ``mixed_compressed_allreduce`` is
 the hierarchical allreduce (raw inside a node, compressed between nodes);
 ``allreduce_ring_gpu`` the uncompressed device allreduce.
 """
@@ -17,7 +17,7 @@ import torch
 import torch.distributed as dist
 
 from .comm import CompressedAllreduce
-from .cpu_ring import cpu_compressed_allreduce
+from .cpu_ring import cpu_compressed_allreduce  # noqa: F401  (host-only counterpart)
 
 
 def allreduce_ring_comprs_hom_sum_F(comm: CompressedAllreduce, d_sbuf, d_rbuf, eb: float):
@@ -44,13 +44,86 @@ def _host_group(group):
     return _host_groups[key]
 
 
+_codecs = {}
+
+
+def _codec_for(device, max_elems):
+    from ..ops import Codec
+
+    key = (str(device), int(max_elems))
+    if key not in _codecs:
+        _codecs[key] = Codec(max_elems, device=device)
+    return _codecs[key]
+
+
 def cpuCopy_allreduce_ring_comprs_hom_sum_F(d_sbuf: torch.Tensor, d_rbuf: torch.Tensor, eb: float, host_group=None):
-    """Host-staged compressed allreduce: every message crosses the host (pinned bounce buffers)."""
+    """Host-staged compressed ring allreduce for GPUs that cannot address each other: the codec and
+    the fused homomorphic add run on the device, every compressed chunk is copied to pinned host
+    memory, travels over the host network (gloo) and is copied back up (the reference's
+    non-CUDA-aware variants, HomComp/src/nca_allreduce.cu:195-324).  Same partition, hop order and
+    arithmetic as the device ring, hence the same bits."""
+    from .. import ops
+    from .cpu_ring import _recv, _send
+
     g = host_group if host_group is not None else _host_group(None)
-    host = torch.empty(d_sbuf.numel(), dtype=torch.float32).pin_memory()
-    host.copy_(d_sbuf)
-    out = cpu_compressed_allreduce(host.numpy(), eb, group=g)
-    d_rbuf.copy_(torch.from_numpy(out))
+    P, r = dist.get_world_size(g), dist.get_rank(g)
+    n = d_sbuf.numel()
+    B = ops.chunk_elems(n, P)
+    dev = d_sbuf.device
+    codec = _codec_for(dev, B)
+    src = d_sbuf.reshape(-1)
+    dst = d_rbuf.reshape(-1)
+    cap = ops.max_compressed_bytes(B) + 64
+    bounce = torch.empty(cap, dtype=torch.uint8).pin_memory()
+
+    def chunk(c):
+        return src[c * B: min((c + 1) * B, n)]
+
+    def down(stream, size):  # device stream -> host bytes (the size is the one host read per hop)
+        nbytes = int(size.item())
+        bounce[:nbytes].copy_(stream[:nbytes])
+        return bounce[:nbytes].numpy().copy()
+
+    def up(arr):  # host bytes -> device stream, with the slack the bulk copies may read past the end
+        t = torch.zeros(arr.size + 64, dtype=torch.uint8, device=dev)
+        if arr.size:
+            t[: arr.size].copy_(torch.from_numpy(arr))
+        return t
+
+    def exchange(out_bytes, what):  # even ranks send first, odd ranks receive first
+        if r % 2 == 0:
+            _send(out_bytes, (r + 1) % P, g)
+            return _recv((r - 1) % P, g, what)
+        incoming = _recv((r - 1) % P, g, what)
+        _send(out_bytes, (r + 1) % P, g)
+        return incoming
+
+    import numpy as np
+
+    empty = np.zeros(0, dtype=np.uint8)
+    held = down(*codec.compress(chunk(r), eb)) if chunk(r).numel() else empty
+    for s in range(1, P):
+        incoming = exchange(held, "reduce-scatter step %d" % s) if P > 1 else held
+        c = (r - s) % P
+        m = chunk(c).numel()
+        if m == 0:
+            held = empty
+        elif incoming.size:
+            held = down(*codec.hom_add(up(incoming), chunk(c), eb, stream_bytes=incoming.size))
+        else:
+            held = down(*codec.compress(chunk(c), eb))
+    held_c = (r + 1) % P
+    streams = {held_c: held}
+    for s in range(P - 1):
+        held = exchange(held, "all-gather step %d" % s)
+        held_c = (held_c - 1) % P
+        streams[held_c] = held
+    for c, st in streams.items():
+        m = chunk(c).numel()
+        if m:
+            codec.decompress(up(st), m, eb, out=dst[c * B: c * B + m], stream_bytes=st.size)
+    if codec.status() != 0:
+        raise RuntimeError("host-staged allreduce: device codec reported an error")
     return d_rbuf
 
 
