@@ -162,6 +162,19 @@ int mixed_compressed_allreduce(float* s, float* r, size_t count, MPI_Comm comm, 
 }
 int allreduce_ring_gpu(const float* s, float* r, size_t count, MPI_Comm comm) { return hc_allreduce_raw(comm, s, r, count, 0); }
 
+int cpuCopy_allreduce_ring_comprs_hom_sum_F(const float* s, float* r, size_t count, MPI_Comm comm, float eb) {
+  return hc_comm_allreduce_host_staged(comm, s, r, count, eb, 0);
+}
+int cpuCopy_allreduce_ring_comprs_hom_sum(const float* s, float* r, size_t count, MPI_Comm comm, float eb) {
+  return cpuCopy_allreduce_ring_comprs_hom_sum_F(s, r, count, comm, eb);
+}
+int cpuCopy_allreduce_ring_comprs_hom_sum_seg(const float* s, float* r, size_t count, MPI_Comm comm, float eb) {
+  return cpuCopy_allreduce_ring_comprs_hom_sum_F(s, r, count, comm, eb);
+}
+int cpuCopy_allreduce_ring_comprs_hom_sum_F_seg(const float* s, float* r, size_t count, MPI_Comm comm, float eb) {
+  return cpuCopy_allreduce_ring_comprs_hom_sum_F(s, r, count, comm, eb);
+}
+
 float* read_binary_floats(const char* filename, size_t* out_size) {
   if (out_size) *out_size = 0;
   FILE* f = fopen(filename, "rb");

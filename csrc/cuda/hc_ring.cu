@@ -77,6 +77,8 @@ struct hc_comm {
   int algorithm = 1;              // 0 ring (P + 1 kernels), 1 direct (3 kernels)
   bool trace = false;             // record one CUDA event per step of hc_allreduce
   bool overlap = true;            // direct algorithm: steps 2 and 3 start while their predecessor drains
+  hc_host_transport host_tp = {nullptr, nullptr, nullptr};  // for the host-staged variant
+  hc_codec* host_codec = nullptr;                           // created on its first use
   cudaEvent_t ev[hc::kMaxDst + 3] = {};
   int n_ev = 0;
   uint64_t spin_limit_ns = 2000ull * 1000 * 1000;
@@ -166,6 +168,7 @@ void hc_comm_destroy(hc_comm* c) {
     if (e) cudaEventDestroy(e);
   if (c->ws_mem) cudaFree(c->ws_mem);
   if (c->sizes) cudaFree(c->sizes);
+  if (c->host_codec) hc_codec_destroy(c->host_codec);
   delete c;
 }
 
@@ -412,6 +415,23 @@ extern "C" int hc_comm_set_algorithm(hc_comm* c, int algorithm) {
   if (!c || algorithm < 0 || algorithm > 1) return hc::kErrArgument;
   c->algorithm = algorithm;
   return hc::kOk;
+}
+
+extern "C" int hc_comm_set_host_transport(hc_comm* c, const hc_host_transport* t) {
+  if (!c || !t || !t->send || !t->recv) return hc::kErrArgument;
+  c->host_tp = *t;
+  return hc::kOk;
+}
+
+extern "C" int hc_comm_allreduce_host_staged(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, float eb,
+                                             hc_stream_t stream) {
+  if (!c || !c->host_tp.send || count > c->max_count) return hc::kErrArgument;
+  if (!c->host_codec) {
+    const size_t per_rank = hc_chunk_elems(c->max_count, c->world);
+    if (hc_codec_create(&c->host_codec, per_rank) != hc::kOk) return hc::kErrCuda;
+    hc_codec_set_timeout_ms(c->host_codec, (unsigned)(c->spin_limit_ns / 1000000ull));
+  }
+  return hc_allreduce_host_staged(c->host_codec, &c->host_tp, c->rank, c->world, d_sbuf, d_rbuf, count, eb, stream);
 }
 
 extern "C" int hc_comm_set_overlap(hc_comm* c, int on) {

@@ -137,6 +137,28 @@ int hc_comm_last_step_ms(hc_comm* c, float* ms, int n);
 // device-side counters of the last call: bytes[s] = stream bytes this rank produced at step s
 int hc_comm_last_stream_bytes(hc_comm* c, uint64_t* bytes, int n);
 
+// ---- host-staged compressed allreduce (GPUs that cannot address each other) ---------------------
+// The codec and the fused add run on the device; every compressed chunk goes through pinned host
+// memory and the caller's transport.  send/recv move one message to / from rank dst / src and
+// return 0 on success (recv stores the message length in *bytes; a message never exceeds cap).
+// Ranks with an even number send first, the others receive first, so a blocking transport is
+// fine.  Synchronises the host once per hop and allocates its bounce buffers per call, like the
+// reference's cpuCopy_* variants (HomComp/src/nca_allreduce.cu:195-324).  `codec` must have been
+// created for at least hc_chunk_elems(count, world) values.
+typedef int (*hc_send_fn)(void* user, int dst, const void* buf, size_t bytes);
+typedef int (*hc_recv_fn)(void* user, int src, void* buf, size_t cap, size_t* bytes);
+typedef struct hc_host_transport {
+  hc_send_fn send;
+  hc_recv_fn recv;
+  void* user;
+} hc_host_transport;
+int hc_allreduce_host_staged(hc_codec* codec, const hc_host_transport* t, int rank, int world, const float* d_sbuf,
+                             float* d_rbuf, size_t count, float eb, hc_stream_t stream);
+// Registers the transport that the cpuCopy_* names of homcomp_compat.h use with this communicator.
+int hc_comm_set_host_transport(hc_comm* c, const hc_host_transport* t);
+int hc_comm_allreduce_host_staged(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, float eb,
+                                  hc_stream_t stream);
+
 // CUDA IPC helpers for the multi-process bootstrap (the 64-byte handle travels over any host
 // channel: torch.distributed, MPI, a file)
 int hc_ipc_alloc(void** d_ptr, size_t bytes, uint8_t handle[64]);

@@ -52,6 +52,13 @@ int allreduce_ring_comprs_hom_sum_F_seg(const float* d_sbuf, float* d_rbuf, size
 int allreduce_ring_comprs_hom_sum_F_opt(const float* d_sbuf, float* d_rbuf, size_t count, MPI_Comm comm, float eb);
 int mixed_compressed_allreduce(float* d_sbuf, float* d_rbuf, size_t count, MPI_Comm comm, float eb);
 int allreduce_ring_gpu(const float* d_sbuf, float* d_rbuf, size_t count, MPI_Comm comm);
+// host-staged variants (HomComp/include/nca_allreduce.cuh:3-15): one engine, see
+// hc_allreduce_host_staged; the communicator needs a transport (hc_comm_set_host_transport)
+int cpuCopy_allreduce_ring_comprs_hom_sum(const float* d_sbuf, float* d_rbuf, size_t count, MPI_Comm comm, float eb);
+int cpuCopy_allreduce_ring_comprs_hom_sum_F(const float* d_sbuf, float* d_rbuf, size_t count, MPI_Comm comm, float eb);
+int cpuCopy_allreduce_ring_comprs_hom_sum_seg(const float* d_sbuf, float* d_rbuf, size_t count, MPI_Comm comm, float eb);
+int cpuCopy_allreduce_ring_comprs_hom_sum_F_seg(const float* d_sbuf, float* d_rbuf, size_t count, MPI_Comm comm,
+                                                float eb);
 #endif
 
 // whole-file read of raw float32 values into malloc'd memory (caller frees)

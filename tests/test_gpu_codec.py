@@ -190,3 +190,44 @@ def test_multi_stream_add_about_one_tile_per_cta(k, n):
         out, size = codec.hom_add_multi(gs, _gpu(y), eb, stream_bytes=[s.size for s in streams])
         assert codec.status() == 0
         np.testing.assert_array_equal(_stream(out, size), want)
+
+
+@pytest.mark.parametrize("world,n", [(1, 5000), (2, 100_003), (3, 300_000), (4, 33)])
+def test_native_host_staged_ring_between_threads(world, n):
+    """hc_allreduce_host_staged with queues between threads as the transport: every rank is a host
+    thread with its own codec handle on the one GPU (no kernel waits for another one here: all
+    waiting is done by the host threads)."""
+    import queue
+    import threading
+
+    from tirocinio_triennale_b200.parallel import collectives
+
+    eb = 1e-4
+    bufs = [ALL["gradient" if r % 2 else "smooth"](n, seed=40 + r) for r in range(world)]
+    want = ops.cpu_ring_allreduce(bufs, eb)
+    xs = [_gpu(b) for b in bufs]
+    outs = [torch.full_like(x, -7.0) for x in xs]
+    codecs = [ops.Codec(ops.chunk_elems(n, world) + 64) for _ in range(world)]
+    streams = [torch.cuda.Stream() for _ in range(world)]
+    links = {(a, b): queue.Queue() for a in range(world) for b in range(world)}
+    errors = []
+
+    def rank_main(r):
+        try:
+            with torch.cuda.stream(streams[r]):
+                collectives.host_staged_allreduce_native(
+                    codecs[r], r, world, lambda dst, data: links[(r, dst)].put(data),
+                    lambda src: links[(src, r)].get(timeout=20), xs[r], outs[r], eb)
+        except Exception as e:  # noqa: BLE001
+            errors.append((r, repr(e)))
+
+    torch.cuda.synchronize()
+    threads = [threading.Thread(target=rank_main, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(60)
+    assert not errors and not any(t.is_alive() for t in threads), errors
+    torch.cuda.synchronize()
+    for r in range(world):
+        np.testing.assert_array_equal(outs[r].cpu().numpy(), want[r])

@@ -5,6 +5,13 @@ import ctypes as C
 
 vp = C.c_void_p
 
+SEND_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t)
+RECV_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t))
+
+
+class HostTransport(C.Structure):
+    _fields_ = [("send", SEND_FN), ("recv", RECV_FN), ("user", C.c_void_p)]
+
 
 def declare(lib):
     sz, f, i, u = C.c_size_t, C.c_float, C.c_int, C.c_uint
@@ -23,6 +30,9 @@ def declare(lib):
         "hc_comm_set_overlap": [vp, i],
         "hc_comm_last_step_ms": [vp, C.POINTER(C.c_float), i],
         "hc_comm_last_stream_bytes": [vp, C.POINTER(C.c_uint64), i],
+        "hc_allreduce_host_staged": [vp, C.POINTER(HostTransport), i, i, vp, vp, sz, f, vp],
+        "hc_comm_set_host_transport": [vp, C.POINTER(HostTransport)],
+        "hc_comm_allreduce_host_staged": [vp, vp, vp, sz, f, vp],
         "hc_ipc_alloc": [C.POINTER(vp), sz, C.c_char_p],
         "hc_ipc_open": [C.c_char_p, C.POINTER(vp)],
         "hc_ipc_close": [vp],

@@ -127,6 +127,44 @@ def cpuCopy_allreduce_ring_comprs_hom_sum_F(d_sbuf: torch.Tensor, d_rbuf: torch.
     return d_rbuf
 
 
+def host_staged_allreduce_native(codec, rank: int, world: int, send, recv, d_sbuf: torch.Tensor,
+                                 d_rbuf: torch.Tensor, eb: float):
+    """The library's own host-staged ring (``hc_allreduce_host_staged``) over a transport given as two
+    Python callables: ``send(dst: int, data: bytes)`` and ``recv(src: int) -> bytes``.  The device
+    codec ``codec`` (``ops.Codec`` for at least ``chunk_elems(n, world)`` values) does the work."""
+    import ctypes as C
+
+    from .. import _lib
+    from .._lib_ext import RECV_FN, SEND_FN, HostTransport
+
+    def _send(_user, dst, buf, nbytes):
+        try:
+            send(int(dst), C.string_at(buf, nbytes) if nbytes else b"")
+            return 0
+        except Exception:  # noqa: BLE001  (reported to the C side as a peer failure)
+            return 1
+
+    def _recv(_user, src, buf, cap, out_bytes):
+        try:
+            data = recv(int(src))
+            if len(data) > cap:
+                return 2
+            if data:
+                C.memmove(buf, data, len(data))
+            out_bytes[0] = len(data)
+            return 0
+        except Exception:  # noqa: BLE001
+            return 1
+
+    tp = HostTransport(SEND_FN(_send), RECV_FN(_recv), None)
+    lib = _lib.cuda()
+    with torch.cuda.device(d_sbuf.device):
+        rc = lib.hc_allreduce_host_staged(codec._h, C.byref(tp), rank, world, d_sbuf.data_ptr(), d_rbuf.data_ptr(),
+                                          d_sbuf.numel(), eb, torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "host-staged allreduce")
+    return d_rbuf
+
+
 cpuCopy_allreduce_ring_comprs_hom_sum = cpuCopy_allreduce_ring_comprs_hom_sum_F
 cpuCopy_allreduce_ring_comprs_hom_sum_seg = cpuCopy_allreduce_ring_comprs_hom_sum_F
 cpuCopy_allreduce_ring_comprs_hom_sum_F_seg = cpuCopy_allreduce_ring_comprs_hom_sum_F
