@@ -2,7 +2,9 @@
 // peer access between all of them, the reference-named collective API (homcomp_compat.h).  Every
 // rank holds the same data, so the expected result is world * input; the check is the
 // reference checker's rule |world * in - out| <= 2 eb (world + world / 10)
-// (HomComp/src/utils/checksmooth.c:50-51).  Prints device-timed latency per mode.
+// (HomComp/src/utils/checksmooth.c:50-51).  Prints device-timed latency per mode: compressed over
+// peer memory, uncompressed, and host-staged (cpuCopy_* names) with mailboxes between the threads
+// standing in for the host network.
 //
 //   allreduce_threads [gpus] [count] [eb] [iterations]
 #include <cuda_runtime.h>
@@ -10,7 +12,13 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+#include <string.h>
+
 #include <atomic>
+#include <chrono>
+#include <condition_variable>
+#include <deque>
+#include <mutex>
 #include <thread>
 #include <vector>
 
@@ -31,6 +39,41 @@ struct Barrier {
   }
 };
 
+// one mailbox per (source, destination) pair: the "host network" of the host-staged mode
+struct Mailbox {
+  std::mutex m;
+  std::condition_variable cv;
+  std::deque<std::vector<unsigned char>> q;
+};
+struct Net {
+  int P, rank;
+  std::vector<Mailbox>* boxes;  // [src * P + dst]
+};
+static int net_send(void* user, int dst, const void* buf, size_t bytes) {
+  Net* n = static_cast<Net*>(user);
+  Mailbox& b = (*n->boxes)[(size_t)n->rank * n->P + dst];
+  std::vector<unsigned char> msg(bytes);
+  if (bytes) memcpy(msg.data(), buf, bytes);
+  {
+    std::lock_guard<std::mutex> g(b.m);
+    b.q.push_back(std::move(msg));
+  }
+  b.cv.notify_one();
+  return 0;
+}
+static int net_recv(void* user, int src, void* buf, size_t cap, size_t* bytes) {
+  Net* n = static_cast<Net*>(user);
+  Mailbox& b = (*n->boxes)[(size_t)src * n->P + n->rank];
+  std::unique_lock<std::mutex> g(b.m);
+  if (!b.cv.wait_for(g, std::chrono::seconds(20), [&] { return !b.q.empty(); })) return 1;  // the peer never sent
+  std::vector<unsigned char> msg = std::move(b.q.front());
+  b.q.pop_front();
+  if (msg.size() > cap) return 2;
+  if (!msg.empty()) memcpy(buf, msg.data(), msg.size());
+  *bytes = msg.size();
+  return 0;
+}
+
 int main(int argc, char** argv) {
   int ndev = 0;
   cudaGetDeviceCount(&ndev);
@@ -47,7 +90,8 @@ int main(int argc, char** argv) {
   const size_t sym = hc_comm_symmetric_bytes(P, count);
   std::vector<void*> region(P, nullptr);
   std::vector<int> failures(P, 0);
-  std::vector<float> lat_c(P, 0), lat_r(P, 0);
+  std::vector<float> lat_c(P, 0), lat_r(P, 0), lat_h(P, 0);
+  std::vector<Mailbox> boxes((size_t)P * P);
   Barrier bar(P);
   auto worker = [&](int r) {
     int sense = 0;
@@ -60,6 +104,9 @@ int main(int argc, char** argv) {
     bar.wait(sense);
     hc_comm* comm = nullptr;
     if (hc_comm_create(&comm, r, P, count, region.data(), nullptr) != 0) { failures[r] = 1; return; }
+    Net net{P, r, &boxes};
+    hc_host_transport tp{net_send, net_recv, &net};
+    if (hc_comm_set_host_transport(comm, &tp) != 0) failures[r] = 1;
     float *d_in, *d_out;
     cudaMalloc(&d_in, count * 4);
     cudaMalloc(&d_out, count * 4);
@@ -68,22 +115,23 @@ int main(int argc, char** argv) {
     cudaEventCreate(&e0);
     cudaEventCreate(&e1);
     std::vector<float> out(count);
-    for (int mode = 0; mode < 2; ++mode) {
+    for (int mode = 0; mode < 3; ++mode) {
       float total = 0, ms;
       for (int it = 0; it < iters + 2; ++it) {
         bar.wait(sense);
         cudaEventRecord(e0);
-        int rc = mode == 0 ? allreduce_ring_comprs_hom_sum_F(d_in, d_out, count, comm, eb)
-                           : allreduce_ring_gpu(d_in, d_out, count, comm);
+        int rc = mode == 0   ? allreduce_ring_comprs_hom_sum_F(d_in, d_out, count, comm, eb)
+                 : mode == 1 ? allreduce_ring_gpu(d_in, d_out, count, comm)
+                             : cpuCopy_allreduce_ring_comprs_hom_sum_F(d_in, d_out, count, comm, eb);
         cudaEventRecord(e1);
         cudaEventSynchronize(e1);
         cudaEventElapsedTime(&ms, e0, e1);
         if (rc) failures[r] = 1;
         if (it >= 2) total += ms;
       }
-      (mode == 0 ? lat_c : lat_r)[r] = total / iters;
+      (mode == 0 ? lat_c : mode == 1 ? lat_r : lat_h)[r] = total / iters;
       cudaMemcpy(out.data(), d_out, count * 4, cudaMemcpyDeviceToHost);
-      const double tol = mode == 0 ? 2.0 * eb * (P + P / 10.0) : 1e-5 * P;
+      const double tol = mode != 1 ? 2.0 * eb * (P + P / 10.0) : 1e-5 * P;
       size_t bad = 0;
       for (size_t i = 0; i < count; ++i)
         if (fabs((double)host[i] * P - out[i]) > tol) ++bad;
@@ -100,14 +148,16 @@ int main(int argc, char** argv) {
   std::vector<std::thread> th;
   for (int r = 0; r < P; ++r) th.emplace_back(worker, r);
   for (auto& t : th) t.join();
-  float mc = 0, mr = 0;
+  float mc = 0, mr = 0, mh = 0;
   int fail = 0;
   for (int r = 0; r < P; ++r) {
     mc = lat_c[r] > mc ? lat_c[r] : mc;
     mr = lat_r[r] > mr ? lat_r[r] : mr;
+    mh = lat_h[r] > mh ? lat_h[r] : mh;
     fail |= failures[r];
   }
-  printf("gpus %d count %zu eb %g | compressed allreduce %.3f ms (%.1f GB/s) | uncompressed %.3f ms (%.1f GB/s) | %s\n", P,
-         count, eb, mc, 4e-6 * count / mc, mr, 4e-6 * count / mr, fail ? "FAILED" : "ok");
+  printf("gpus %d count %zu eb %g | compressed allreduce %.3f ms (%.1f GB/s) | uncompressed %.3f ms (%.1f GB/s) | "
+         "host-staged %.3f ms | %s\n",
+         P, count, eb, mc, 4e-6 * count / mc, mr, 4e-6 * count / mr, mh, fail ? "FAILED" : "ok");
   return fail;
 }
