@@ -26,8 +26,8 @@
 // global-memory round trip of their own.  Look-back status words are 64-bit and epoch-tagged:
 // the workspace is never cleared between launches, and the exact stream size lands in device
 // memory (no host round trip).  The grid never exceeds what the GPU holds at once, so every tile's
-// predecessors are in the hands of CTAs that run or have finished, whatever the scheduling order;
-// every wait is bounded all the same.
+// predecessors are in the hands of CTAs that run, have finished, or are next in line for an SM slot
+// (other kernels on the GPU can delay them, not starve them); every wait is bounded all the same.
 //
 // The reference runs one warp per CTA, one thread per 32 blocks with a 4 KB local-memory array per
 // thread, and needs a 4-byte device-to-host copy after every launch
