@@ -12,7 +12,6 @@
 #include <stdint.h>
 #include <string.h>
 
-#include <vector>
 
 #include "hc_format.h"
 #include "homcomp_b200.h"
