@@ -231,3 +231,19 @@ def test_native_host_staged_ring_between_threads(world, n):
     torch.cuda.synchronize()
     for r in range(world):
         np.testing.assert_array_equal(outs[r].cpu().numpy(), want[r])
+
+
+def test_stream_files_cross_between_device_and_host(tmp_path):
+    """A tensor written from the GPU reads back on the CPU and the other way round: same bytes."""
+    from tirocinio_triennale_b200.ops import stream_io
+
+    eb = 1e-4
+    t = torch.from_numpy(ALL["gradient"](70_000, seed=7)).reshape(7, 10_000)
+    stream_io.save_tensor(tmp_path / "gpu.hcz", t.cuda(), eb)
+    stream_io.save_tensor(tmp_path / "cpu.hcz", t, eb)
+    assert (tmp_path / "gpu.hcz").read_bytes() == (tmp_path / "cpu.hcz").read_bytes()
+    on_cpu = stream_io.load_tensor(tmp_path / "gpu.hcz")
+    on_gpu = stream_io.load_tensor(tmp_path / "cpu.hcz", device="cuda")
+    assert on_gpu.is_cuda and on_gpu.shape == t.shape
+    assert torch.equal(on_gpu.cpu(), on_cpu)
+    assert (on_cpu - t).abs().max().item() <= eb * 1.0001

@@ -70,7 +70,7 @@ def _decompress(stream: np.ndarray, n: int, eb: float, mode: str, device) -> tor
         from .codec import Codec
 
         codec = Codec(n, device=device)
-        s = torch.from_numpy(np.ascontiguousarray(stream)).to(device)
+        s = torch.from_numpy(np.array(stream, dtype=np.uint8, copy=True)).to(device)  # the file buffer is read-only
         return codec.decompress(s, n, eb, mode=mode, stream_bytes=stream.size)
     return torch.from_numpy(cpu_codec.cpu_decompress(stream, n, eb, mode=mode))
 
