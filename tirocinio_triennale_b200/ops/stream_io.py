@@ -70,7 +70,11 @@ def _decompress(stream: np.ndarray, n: int, eb: float, mode: str, device) -> tor
         from .codec import Codec
 
         codec = Codec(n, device=device)
-        s = torch.from_numpy(np.array(stream, dtype=np.uint8, copy=True)).to(device)  # the file buffer is read-only
+        # own copy (the file buffer is read-only) with the slack that the kernel's 16-byte aligned
+        # bulk copies may read past the last payload byte
+        padded = np.zeros(stream.size + 64, dtype=np.uint8)
+        padded[: stream.size] = stream
+        s = torch.from_numpy(padded).to(device)
         return codec.decompress(s, n, eb, mode=mode, stream_bytes=stream.size)
     return torch.from_numpy(cpu_codec.cpu_decompress(stream, n, eb, mode=mode))
 
