@@ -52,6 +52,9 @@ size_t hc_chunk_elems(size_t count, int P);
 // `stream`: they never allocate, never synchronise and never copy to the host.  The exact stream
 // length is written to the device word d_size.  One codec handle serialises on one stream at a
 // time (its workspace holds the look-back state of the launch in flight).
+// Input streams are read with 16-byte aligned bulk copies: the buffer that holds a stream must be
+// readable up to the next 16-byte boundary past its last byte (true of any device allocation whose
+// size is a multiple of 16, e.g. one of hc_max_compressed_bytes(n) rounded up).
 typedef struct CUstream_st* hc_stream_t;  // same type as cudaStream_t
 typedef struct hc_codec hc_codec;
 
