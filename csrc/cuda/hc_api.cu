@@ -14,6 +14,7 @@ struct hc_codec {
   bool owns = false;
   uint32_t epoch = 0;
   uint64_t spin_limit_ns = 2000ull * 1000 * 1000;
+  bool prepass = true;  // large stand-alone inputs: tile offsets from a pre-pass instead of an input look-back
 };
 
 namespace {
@@ -26,6 +27,33 @@ hc::Workspace next_workspace(hc_codec* c, cudaStream_t stream) {
     c->epoch = 1;
   }
   return hc::workspace_view(c->ws_mem, c->max_elems, c->epoch, c->spin_limit_ns);
+}
+
+// Streams of at least this many tiles get their tile offsets from the pre-pass (launch_offsets):
+// below it the consuming kernel has a tile or two per CTA and its own look-back costs nothing extra.
+constexpr uint32_t kPrepassMinTiles = 1024;
+
+// Enqueues the pre-pass over `n_in` streams of n values each and returns the flag rows it fills
+// (in the look-back words of the input chains, which the consumer then does not use); false when the
+// streams are small or the workspace has no room, in which case the consumer walks the chains itself.
+bool stage_offsets(hc_codec* c, const hc::Workspace& ws, const uint8_t* const* in, const size_t* in_size, uint32_t n_in,
+                   size_t n, const uint64_t** flags, cudaStream_t stream) {
+  const uint32_t tiles = (uint32_t)(hc::rate_bytes(n) / hc::kTileBlocks);
+  if (!c->prepass || tiles < kPrepassMinTiles || !hc::offsets_fit(ws, c->max_elems, n_in, tiles)) return false;
+  hc::OffsetParams o;
+  memset(&o, 0, sizeof(o));
+  o.n_in = n_in;
+  o.tiles_per_seg = tiles;
+  o.nrate = hc::rate_bytes(n);
+  o.tag = ws.epoch;  // below 2^22: can never match a look-back status word left in the same place
+  o.ws = ws;
+  for (uint32_t q = 0; q < n_in; ++q) {
+    o.in[q] = in[q];
+    o.in_size[q] = in_size[q];
+    o.flags[q] = ws.st_a + (size_t)q * tiles;
+    flags[q] = o.flags[q];
+  }
+  return hc::launch_offsets(o, stream) == cudaSuccess;
 }
 
 int check_call(hc_codec* c, size_t n, float eb, bool needs_eb) {
@@ -59,7 +87,16 @@ int encode_call(hc_codec* c, int op, int mode, const void* local, const uint8_t*
   p.out_cap = cap;
   p.size_out = d_size;
   p.ws = next_workspace(c, stream);
-  return hc::launch_encode(op, mode, p, stream) == cudaSuccess ? hc::kOk : hc::kErrCuda;
+  bool flagged = false;
+  if (p.n_in) {
+    const uint8_t* ins[2] = {in, in2};
+    const size_t sizes[2] = {in_size, in2_size};
+    flagged = stage_offsets(c, p.ws, ins, sizes, p.n_in, n, p.in_ready, stream);
+    if (flagged) p.ring_epoch = p.ws.epoch;
+    else p.in_ready[0] = p.in_ready[1] = nullptr;
+  }
+  // behind its pre-pass the kernel starts at once and consumes tiles as their flags appear
+  return hc::launch_encode(op, mode, p, stream, flagged) == cudaSuccess ? hc::kOk : hc::kErrCuda;
 }
 
 }  // namespace
@@ -107,6 +144,20 @@ void hc_codec_destroy(hc_codec* c) {
 int hc_codec_set_timeout_ms(hc_codec* c, unsigned ms) {
   if (!c || ms == 0) return hc::kErrArgument;
   c->spin_limit_ns = (uint64_t)ms * 1000ull * 1000ull;
+  return hc::kOk;
+}
+
+int hc_codec_status_site(hc_codec* c) {
+  if (!c) return -1;
+  uint32_t ctrl[4] = {0, 0, 0, 0};
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpy(ctrl, c->ws_mem, sizeof(ctrl), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return (int)ctrl[3];
+}
+
+int hc_codec_set_prepass(hc_codec* c, int on) {
+  if (!c) return hc::kErrArgument;
+  c->prepass = on != 0;
   return hc::kOk;
 }
 
@@ -159,7 +210,13 @@ static int decompress_call(hc_codec* c, const uint8_t* d_in, size_t in_size, siz
   p.ring_epoch = want;
   p.eb = eb;
   p.ws = next_workspace(c, stream);
-  return hc::launch_decode(mode, p, stream) == cudaSuccess ? hc::kOk : hc::kErrCuda;
+  bool flagged = false;
+  if (!d_tile_flags) {
+    flagged = stage_offsets(c, p.ws, &d_in, &in_size, 1, n, &p.seg[0].in_ready, stream);
+    if (flagged) p.ring_epoch = p.ws.epoch;
+    else p.seg[0].in_ready = nullptr;
+  }
+  return hc::launch_decode(mode, p, stream, flagged) == cudaSuccess ? hc::kOk : hc::kErrCuda;
 }
 
 int hc_decompress(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, float eb, int mode, float* d_x,
@@ -223,7 +280,11 @@ int hc_hom_add_multi(hc_codec* c, int n_in, const uint8_t* const* d_in, const si
   p.out_cap = cap;
   p.size_out = d_size;
   p.ws = next_workspace(c, stream);
-  return hc::launch_encode(hc::kOpAddF32, mode, p, stream) == cudaSuccess ? hc::kOk : hc::kErrCuda;
+  const bool flagged = stage_offsets(c, p.ws, d_in, in_size, p.n_in, n, p.in_ready, stream);
+  if (flagged) p.ring_epoch = p.ws.epoch;
+  else
+    for (int q = 0; q < n_in; ++q) p.in_ready[q] = nullptr;
+  return hc::launch_encode(hc::kOpAddF32, mode, p, stream, flagged) == cudaSuccess ? hc::kOk : hc::kErrCuda;
 }
 
 int hc_quant_pred(const float* d_x, size_t n, float eb, int mode, int32_t* d_deltas, hc_stream_t stream) {

@@ -12,22 +12,28 @@ constexpr int kEncThreads = kComputeThreads + 64;  // + loader warp + scanner wa
 constexpr int kDecThreads = kComputeThreads + 32;  // + loader warp
 constexpr uint32_t kNoTile = 0xffffffffu;
 
-constexpr int kMaxStages = 4;
+constexpr int kMaxStages = 2;
+constexpr int kRing = 8;  // tiles a CTA may have between "total known" and "payload copied out"
 struct __align__(16) EncShared {
   uint64_t tma_full[kMaxStages];    // fp32 tile landed in stage s (or "nothing to fetch"); also hands over the ticket
-  uint64_t stage_free[kMaxStages];  // compute threads have moved the packed tile out of stage s
-  uint64_t scan_done[kMaxStages];   // tile total known: the scanner may start its look-back
-  uint64_t base_ready[kMaxStages];  // look-back of the tile in stage s finished: out_base / out_ok valid
+  uint64_t stage_free[kMaxStages];  // every compute thread holds its row of the tile in registers: refill the stage
+  uint64_t scan_done[kRing];        // tile total known: the scanner may start its look-back
+  uint64_t base_ready[kRing];       // look-back of the tile finished: out_base / out_ok valid
   uint64_t in_full[2];              // input stream bytes + meta staged in buffer b
   uint64_t in_free[2];              // compute threads have decoded from buffer b
   uint32_t tile[8];                 // ring of tile tickets, written by the loader
   uint32_t tile_tma[8];             // 1 when a TMA load was issued for that ring slot
   uint32_t in_phase[2];             // 16-byte phase of the staged bytes in buffer b
   uint32_t in_end[2];               // 1: buffer b carries the end marker instead of a stream (ops with inputs)
-  uint32_t out_tot[kMaxStages];     // payload bytes of the tile in stage s
-  uint32_t out_ok[kMaxStages];
-  uint64_t out_base[kMaxStages];    // global byte offset of the tile's payload
+  uint32_t out_tile[kRing];         // ticket of this CTA's k-th tile (kNoTile: end of work), slot k % kRing
+  uint32_t out_tot[kRing];          // its payload bytes
+  uint32_t ring_start[kRing];       // where its payload starts in the ring
+  uint32_t ring_end[kRing];         // first ring byte behind it
+  uint32_t out_ok[kRing];           // 0: the tile is not to be stored (look-back failed, capacity exceeded)
+  uint64_t out_base[kRing];         // byte offset of its payload in the output stream
   uint32_t wsum[2][kComputeThreads / 32];
+  uint32_t copy_upto[2];            // turn k: tiles below copy_upto[k & 1] have their look-back result
+  uint32_t stored_upto;             // tiles below it have been stored by every compute thread
   uint32_t abort;
   uint16_t in_rel[2][kTileBlocks];
   uint8_t in_rate[2][kTileBlocks];
@@ -39,22 +45,41 @@ __device__ __forceinline__ bool fatal_error(const uint32_t* ctrl) {
   return *((volatile const uint32_t*)(ctrl + 2)) >= (uint32_t)kErrTimeout;
 }
 
-// Optional per-CTA timeline (compile with -DHC_TIMELINE): sixteen nanosecond stamps of the first tile's
-// way through the roles, for finding where a launch spends its fixed time.  Not part of a normal build.
+// Optional per-CTA timeline (compile with -DHC_TIMELINE): nanosecond stamps of the first tile's way
+// through the roles (slots 0-15) and, for the first compute warp, SM-clock cycles accumulated per
+// phase of the tile loop (slots 16-30) with the number of tiles in slot 31, for finding where a
+// launch spends its time.  Not part of a normal build.
 #ifdef HC_TIMELINE
-__device__ unsigned long long g_timeline[4 * 1024 * 16];  // [launch epoch & 3][CTA][slot]
+constexpr int kTlSlots = 32;
+__device__ unsigned long long g_timeline[4 * 1024 * kTlSlots];  // [launch epoch & 3][CTA][slot]
 __device__ __forceinline__ unsigned long long timeline_now() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-#define HC_TL_DECL(epoch) \
-  unsigned long long* const hc_tl = g_timeline + (((epoch)&3u) * 1024u + (blockIdx.x < 1024u ? blockIdx.x : 1023u)) * 16u
-#define HC_TL_ZERO() hc_tl[7] = hc_tl[14] = hc_tl[15] = 0
+#define HC_TL_DECL(epoch)                                                                                      \
+  unsigned long long* const hc_tl =                                                                            \
+      g_timeline + (((epoch)&3u) * 1024u + (blockIdx.x < 1024u ? blockIdx.x : 1023u)) * (unsigned)kTlSlots;     \
+  long long hc_ph_t = 0
+#define HC_TL_ZERO()                                \
+  do {                                              \
+    hc_tl[7] = hc_tl[14] = hc_tl[15] = 0;           \
+    for (int i_ = 16; i_ < kTlSlots; ++i_) hc_tl[i_] = 0; \
+  } while (0)
 #define HC_STAMP(i) hc_tl[i] = timeline_now()
 #define HC_STAMP_MAX(i) atomicMax(&hc_tl[i], timeline_now())
 #define HC_TIC() const unsigned long long hc_tic = timeline_now()
 #define HC_TOC(i) hc_tl[i] += timeline_now() - hc_tic
+// phase accounting of one thread: HC_PH_START() once, then HC_PH(i) charges the cycles since the
+// previous mark to phase i
+#define HC_PH_START() hc_ph_t = clock64()
+#define HC_PH(i)                                  \
+  do {                                            \
+    const long long now_ = clock64();             \
+    hc_tl[16 + (i)] += (unsigned long long)(now_ - hc_ph_t); \
+    hc_ph_t = now_;                               \
+  } while (0)
+#define HC_PH_COUNT() hc_tl[kTlSlots - 1] += 1
 #else
 #define HC_TL_DECL(epoch)
 #define HC_TL_ZERO()
@@ -62,6 +87,9 @@ __device__ __forceinline__ unsigned long long timeline_now() {
 #define HC_STAMP_MAX(i)
 #define HC_TIC()
 #define HC_TOC(i)
+#define HC_PH_START()
+#define HC_PH(i)
+#define HC_PH_COUNT()
 #endif
 
 // the last CTA to leave re-arms the ticket counter for the next launch
@@ -79,8 +107,16 @@ __device__ __forceinline__ void cta_epilogue(uint32_t* tick) {
 }
 
 // bounded mbarrier wait that records a timeout
-__device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, const Workspace& ws, volatile uint32_t* abort) {
+// `site` says which wait it was; the first one to run out is kept in ctrl[3] (hc_codec_status_site),
+// because every later time-out of the launch is only a consequence of it
+enum WaitSite : uint32_t {
+  kSiteLoaderStageFree = 1, kSiteLoaderInFree = 2, kSiteComputeInFull = 3, kSiteComputeTile = 4, kSiteComputeRing = 5,
+  kSiteScannerTotal = 6, kSiteCopierBase = 7, kSiteCopierPacked = 8, kSiteDecodeInFree = 9, kSiteDecodeInFull = 10,
+};
+__device__ __forceinline__ bool wait_or_flag(uint64_t* bar, uint32_t parity, const Workspace& ws, volatile uint32_t* abort,
+                                             uint32_t site) {
   if (mbar_wait_bounded(bar, parity, ws.spin_limit_ns)) return true;
+  if (!*abort) atomicCAS(ws.ctrl + 3, 0u, site);
   note_error(ws.ctrl, kErrTimeout);
   *abort = 1;
   return false;
@@ -131,7 +167,7 @@ __device__ __forceinline__ void loader_stage_stream(const uint8_t* in, uint64_t 
     ok = false;
   }
   // the staging buffer (bytes and meta) is free once the compute threads have decoded its previous tile
-  if (wait_free && !wait_or_flag(free_bar, free_parity, ws, abort)) ok = false;
+  if (wait_free && !wait_or_flag(free_bar, free_parity, ws, abort, kSiteLoaderInFree)) ok = false;
   uint32_t rel = inc - sum;
 #pragma unroll
   for (int k = 0; k < kPer; ++k) {
@@ -175,27 +211,44 @@ __device__ __forceinline__ uint64_t flag_wait_warp(const uint64_t* flag, uint32_
 }
 
 // Shared-memory plan of the stream-producing kernel (offsets from a 1024-byte aligned base):
-//   [1 KB guard | stage 0 (16 KB) | 1 KB guard | ... | stage NS-1 | 1 KB guard | cbuf 0 | cbuf 1]
-// A stage first receives the fp32 tile from the TMA unit; once every compute thread holds its row
-// in registers the same bytes become the packing buffer of the tile's payload, which leaves
-// moves out before the loader refills the stage.  NS = 3 when nothing else needs shared memory
-// (compress: 4 CTAs per SM), 2 when an input stream is staged too (3 CTAs per SM), and 1 in the
-// variant for launches with about one tile per CTA, where a fourth CTA per SM is worth more than
-// overlap between a CTA's own tiles (the reduce step of a collective over many ranks).
-constexpr int kStagePitch = kTileBytes + 1024;
-__host__ __device__ constexpr int enc_stages(int op) { return op == kOpCompress ? 3 : 2; }
-__host__ __device__ constexpr int enc_smem_base(int ns) { return 1024 + ns * kStagePitch; }
+//   [1 KB guard | NS fp32 stages of 16 KB | payload ring + 64 guard bytes | cbuf 0 | cbuf 1]
+// A stage receives the fp32 tile from the TMA unit and is free again as soon as every compute thread
+// holds its row in registers.  The packed payload of a tile goes into the RING: a byte ring in which
+// every tile takes just the bytes it needs (about 5 KB of the 16 KB at ratio 3.4), so that several
+// packed tiles can wait there for their look-back while the compute warps go on with the next tiles.
+// The scanner warp moves a tile from the ring to its final byte offset once the offset is known.
+// A tile's look-back waits for the slowest of several hundred predecessor tiles; with the payload
+// parked in the fp32 stage the compute warps of every CTA spent 35-50 % of their time waiting for it.
+// In the IN-PLACE variant (one stage, ring = that stage, 54 KB: four CTAs per SM instead of three for
+// the adds) a tile is packed over its own fp32 data and the stage is refilled after the copy-out:
+// for launches with about one tile per CTA (the reduce step of a collective over many ranks).
+constexpr int kRingBytesCompress = 19392;  // 4 CTAs per SM
+constexpr int kRingBytesAdd = 17920;       // 3 CTAs per SM (shared memory is handed out in 1 KB steps)
+constexpr int kRingBytesInPlace = kTileBytes + 32;
+__host__ __device__ constexpr int enc_stages(int op) { return op == kOpCompress ? 2 : 1; }
+__host__ __device__ constexpr int enc_ring_bytes(int op, bool inplace) {
+  return inplace ? kRingBytesInPlace : (op == kOpCompress ? kRingBytesCompress : kRingBytesAdd);
+}
+// offset of the ring, and of the first staging buffer behind it
+__host__ __device__ constexpr int enc_ring_off(int ns, bool inplace) { return inplace ? 1024 : 1024 + ns * kTileBytes + 16; }
+__host__ __device__ constexpr int enc_cbuf_off(int op, int ns, bool inplace) {
+  return inplace ? 1024 + kTileBytes + 1024 : enc_ring_off(ns, false) + enc_ring_bytes(op, false) + 48;
+}
+static_assert(kRingBytesCompress >= kTileBytes + 32 && kRingBytesAdd >= kTileBytes + 32, "a tile of 128-byte blocks must fit");
 
-template <int OP, int MODE, int NS>
-__global__ void __launch_bounds__(kEncThreads, (OP == kOpCompress || NS == 1) ? 4 : 3)
+template <int OP, int MODE, int NS, bool INPLACE>
+__global__ void __launch_bounds__(kEncThreads, (OP == kOpCompress || INPLACE) ? 4 : 3)
 hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
+  static_assert(NS <= kMaxStages && (!INPLACE || NS == 1), "stage count");
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ EncShared sh;
   constexpr bool kHasLocal = OP != kOpAddStream;
   constexpr bool kHasIn = OP != kOpCompress;
+  constexpr uint32_t kRingBytes = (uint32_t)enc_ring_bytes(OP, INPLACE);
   uint8_t* const stage0 = smem + 1024;
-  uint8_t* cbuf[2] = {smem + enc_smem_base(NS), smem + enc_smem_base(NS) + kBufBytes};
+  uint8_t* const ring = smem + enc_ring_off(NS, INPLACE);
+  uint8_t* cbuf[2] = {smem + enc_cbuf_off(OP, NS, INPLACE), smem + enc_cbuf_off(OP, NS, INPLACE) + kBufBytes};
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -230,6 +283,8 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
     for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(&sh.tma_full[i], 1);
       mbar_init(&sh.stage_free[i], kComputeThreads);
+    }
+    for (int i = 0; i < kRing; ++i) {
       mbar_init(&sh.scan_done[i], 1);
       mbar_init(&sh.base_ready[i], 1);
     }
@@ -242,33 +297,20 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
     HC_TL_ZERO();
     launch_dependents();  // a following launch with programmatic serialisation may fill the SMs as CTAs leave
     sh.in_end[0] = sh.in_end[1] = 0u;
+    sh.stored_upto = 0u;
   }
   __syncthreads();
   volatile uint32_t* abort = &sh.abort;
   if (tid == 0) HC_STAMP(0);
 
-  // The packed payload of a tile leaves one turn late, so that its look-back has a whole tile time
-  // to finish: compress moves tile k-1 out at the end of turn k (three stages); the ops with input
-  // streams move it out in the middle of turn k, between decoding the inputs of tile k (which needs
-  // neither the tile's fp32 stage nor its number) and reading its local operand (two stages: the
-  // stage freed here is refilled for tile k+1 while tile k is quantised and packed).
-  auto move_out = [&](uint32_t j) {  // compute threads: tile number j of this CTA -> global memory
-    const int sj = j % NS;
-    wait_or_flag(&sh.base_ready[sj], (j / NS) & 1, ws, abort);
-    const Seg v = seg_of(sh.tile[j & 7]);
-    if (sh.out_ok[sj])
-      copy_out(stage0 + sj * kStagePitch, p.out + dst_first(v), dst_count(v), sh.out_base[sj], sh.out_tot[sj], tid,
-               kComputeThreads, p.n_seg == 1 ? p.out_mc : nullptr);
-    mbar_arrive(&sh.stage_free[sj]);  // the loader may refill the stage
-  };
   if (warp == kComputeThreads / 32) {
     // ================================ loader warp ================================================
     // Tiles: CTA i starts with tile i (no round trip, and a CTA that starts late, behind a launch
     // that is still draining, finds its tile waiting instead of taken by an early starter); the
     // tiles past the grid come from a shared ticket counter.  Software pipeline over this CTA's
     // tiles: the ticket is taken two turns ahead and the rate bytes of the next input tile one
-    // turn ahead, so neither round trip sits between two look-backs.  Per tile: the input streams first (their aggregates are published before any
-    // wait on this CTA's compute warps), then the fp32 tile's TMA load once its stage is free.
+    // turn ahead, so neither round trip sits between two stagings.  Per tile: the input streams
+    // first, then the fp32 tile's TMA load once its stage is free.
     // Input stream q of this CTA's k-th tile is staging job v = k * Q + q: buffer v & 1.
     auto take = [&]() -> uint32_t {
       uint32_t t = kNoTile;
@@ -319,11 +361,12 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
 #pragma unroll
         for (int i = 0; i < kRatesPerLane; ++i) rates[i] = rates_n[i];
       };
-      // hand-over: the fp32 tile's TMA load into stage s (free once the tile packed there NS turns ago
-      // has been moved out) and the ticket for the compute and scanner warps
+      // hand-over: the fp32 tile's TMA load into stage s (free once the compute threads hold the
+      // rows of the tile that came in NS turns ago; in place: once that tile has been copied out)
+      // and the ticket for the compute warps
       auto hand_over = [&]() -> uint32_t {
         uint32_t t_stage = tile;
-        if (k >= NS && !wait_or_flag(&sh.stage_free[s], ((k / NS) - 1) & 1, ws, abort)) t_stage = kNoTile;
+        if (k >= NS && !wait_or_flag(&sh.stage_free[s], ((k / NS) - 1) & 1, ws, abort, kSiteLoaderStageFree)) t_stage = kNoTile;
         if (lane == 0) {
           sh.tile[slot] = t_stage;
           bool fetch = false;
@@ -333,7 +376,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
             if (fetch) {
               fence_proxy_async();
               mbar_expect_tx(&sh.tma_full[s], kTileBytes);
-              tma_load_2d(stage0 + s * kStagePitch, &tmaps.m[v.g], 0, (int)(v.lt * kTileBlocks), &sh.tma_full[s]);
+              tma_load_2d(stage0 + s * kTileBytes, &tmaps.m[v.g], 0, (int)(v.lt * kTileBlocks), &sh.tma_full[s]);
             }
           }
           sh.tile_tma[slot] = fetch ? 1u : 0u;
@@ -344,7 +387,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       if (kHasIn && tile == kNoTile) {
         // end of work: the compute warps look at the staging buffer first, so the marker goes there
         const uint32_t v = k * Q, b = v & 1u, u = v >> 1;
-        if (u >= 1) wait_or_flag(&sh.in_free[b], (u - 1) & 1, ws, abort);
+        if (u >= 1) wait_or_flag(&sh.in_free[b], (u - 1) & 1, ws, abort, kSiteLoaderInFree);
         if (lane == 0) {
           sh.tile[slot] = kNoTile;
           sh.in_end[b] = 1u;
@@ -353,12 +396,12 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       }
       // The first NS tiles find their stage free: their TMA load goes out before anything else.
       // Afterwards the first two input streams go in first (their buffers only depend on earlier
-      // tiles and free up before the stage does).  Later streams reuse a buffer that the compute
-      // warps free while decoding THIS tile's first streams.
+      // tiles).  Later streams reuse a buffer that the compute warps free while decoding THIS
+      // tile's first streams.
       uint32_t t_stage = kNoTile;
       const bool early = k < (uint32_t)NS;
-      // With a single stage the hand-over waits for the previous tile to leave, which the compute
-      // warps only do after decoding ALL of this tile's streams: every stream goes in first then.
+      // With a single stage the hand-over waits for the compute warps to have read the previous tile,
+      // which they do after decoding ALL of its streams: every stream of this tile goes in first then.
       const uint32_t before = (NS == 1 && !early) ? Q : 2u;
       if (early) t_stage = hand_over();
       if (kHasIn && tile != kNoTile)
@@ -373,14 +416,14 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
     if (lane == 0) HC_STAMP(6);
   } else if (warp == kComputeThreads / 32 + 1) {
     // ================================ scanner warp ===============================================
-    // runs the decoupled look-back of the output stream as soon as a tile's total is known, while
-    // the compute warps are still transposing and packing; hands them the tile's global offset.
-    // In a collective step it also raises the consumers' arrival flags: by the time the compute
-    // warps announce tile k's total, all of them have passed a barrier that follows the stores of
-    // tile k-1 (ops with input streams) or k-2 (compress), so those tiles can be announced.  One
-    // system-scope fence covers a batch of tiles: it waits for the peers' write acknowledgements,
-    // several microseconds over NVLink, and this warp has a tile time of slack that the loader
-    // and the compute warps do not.
+    // runs the decoupled look-back of the output stream as soon as a tile's total is known, while the
+    // compute warps are still transposing and packing, and hands them the tile's byte offset.  Every
+    // other CTA's look-back waits for the words this warp publishes, so it does nothing that could
+    // queue in front of a look-back, with one exception that has slack: in a collective step it
+    // raises the consumers' arrival flags for the tiles the compute warps report as stored
+    // (sh.stored_upto, written behind a barrier that follows the stores).  One system-scope fence
+    // covers a batch of tiles: it waits for the peers' write acknowledgements, several microseconds
+    // over NVLink.
     constexpr uint32_t kFlagBatch = 4;
     const bool raise = p.out_ready[0] != nullptr;  // this launch is a step of a collective
     uint32_t flagged = 0;                           // tiles [0, flagged) of this CTA have been announced
@@ -400,17 +443,20 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       }
       flagged = upto;
     };
+    if (lane == 0) HC_PH_START();
     for (uint32_t k = 0;; ++k) {
-      const int s = k % NS;
-      const uint32_t par = (k / NS) & 1;
-      if (!wait_or_flag(&sh.scan_done[s], par, ws, abort)) break;
-      const uint32_t tile = sh.tile[k & 7];
+      const int r = k % kRing;
+      const uint32_t par = (k / kRing) & 1;
+      if (!wait_or_flag(&sh.scan_done[r], par, ws, abort, kSiteScannerTotal)) break;
+      if (lane == 0) HC_PH(10);
+      const uint32_t tile = sh.out_tile[r];
+      const uint32_t stored = *((volatile uint32_t*)&sh.stored_upto);  // written before scan_done was raised
       if (tile == kNoTile) {
-        raise_flags(k);  // the compute warps have stored every tile before they send the end marker
+        raise_flags(stored);  // the compute warps have stored every tile before they send the end marker
         break;
       }
       const Seg v = seg_of(tile);
-      const uint32_t tot = sh.out_tot[s];
+      const uint32_t tot = sh.out_tot[r];
       bool ok = true;
       const Chain chain{ws.st_out + (size_t)v.g * p.tiles_per_seg, ws.grp_out + (size_t)v.g * groups_per_seg};
       const uint64_t excl = lookback(chain, v.lt, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
@@ -421,25 +467,44 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
         ok = false;
       }
       if (lane == 0) {
-        sh.out_base[s] = goff;
-        sh.out_ok[s] = ok ? 1u : 0u;
-        mbar_arrive(&sh.base_ready[s]);
+        sh.out_base[r] = goff;
+        sh.out_ok[r] = ok ? 1u : 0u;
+        mbar_arrive(&sh.base_ready[r]);
         if (ok && v.lt == p.tiles_per_seg - 1 && p.size_out) p.size_out[v.g] = goff + tot;
         if (fatal_error(ws.ctrl)) *abort = 1;
+        HC_PH(11);
       }
       if ((uint32_t)lane == (k & 31u)) {
         my_lt = v.lt;
         my_g = v.g;
         my_word = flag_pack(p.ring_epoch, ok ? goff : kFlagOffsetMask);
       }
-      const uint32_t out = kHasIn ? k : (k >= 1 ? k - 1 : 0u);  // tiles [0, out) are stored
-      if (out - flagged >= kFlagBatch) raise_flags(out);
+      if (stored - flagged >= kFlagBatch) raise_flags(stored);
     }
   } else {
     // ================================ compute warps ==============================================
+    if (tid == 0) HC_PH_START();
+    uint32_t head = 0;    // next free ring byte (same value in every compute thread)
+    uint32_t copied = 0;  // this CTA's tiles [0, copied) have been moved out of the ring (same in every thread)
+    // all compute threads: tile number j of this CTA -> global memory (its look-back must have finished)
+    auto copy_tile = [&](uint32_t j) {
+      const int rj = j % kRing;
+      const Seg v = seg_of(sh.out_tile[rj]);
+      if (sh.out_ok[rj])
+        copy_out(ring + sh.ring_start[rj], p.out + dst_first(v), dst_count(v), sh.out_base[rj], sh.out_tot[rj],
+                 (uint32_t)tid, (uint32_t)kComputeThreads, p.n_seg == 1 ? p.out_mc : nullptr);
+    };
+    // blocking: tiles [copied, upto) out, whatever their look-backs take
+    auto drain_to = [&](uint32_t upto) {
+      for (uint32_t j = copied; j < upto; ++j) {
+        wait_or_flag(&sh.base_ready[j % kRing], (j / kRing) & 1, ws, abort, kSiteComputeRing);
+        copy_tile(j);
+      }
+      copied = upto > copied ? upto : copied;
+    };
     for (uint32_t k = 0;; ++k) {
-      const int s = k % NS, slot = k & 7;
-      uint8_t* const stage_s = stage0 + s * kStagePitch;
+      const int s = k % NS, slot = k & 7, r = k % kRing;
+      uint8_t* const stage_s = stage0 + s * kTileBytes;
       int32_t d[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) d[i] = 0;
@@ -449,7 +514,8 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       if (kHasIn) {
         for (uint32_t q = 0; q < Q; ++q) {
           const uint32_t vv = k * Q + q, b = vv & 1u;
-          const bool staged = wait_or_flag(&sh.in_full[b], (vv >> 1) & 1, ws, abort);
+          const bool staged = wait_or_flag(&sh.in_full[b], (vv >> 1) & 1, ws, abort, kSiteComputeInFull);
+          if (tid == 0) HC_PH(0);
           if (q == 0 && (!staged || sh.in_end[b])) {
             end = true;  // no tile this turn (or the loader gave up)
             break;
@@ -465,25 +531,32 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
             for (int i = 0; i < 32; ++i) d[i] += d2[i];
           }
           mbar_arrive(&sh.in_free[b]);
+          if (tid == 0) HC_PH(1);
           if (k == 0 && tid == 0 && q < 8) HC_STAMP(8 + q);
         }
-        if (k >= 1) {
-          compute_barrier();  // every thread has packed tile k-1
-          move_out(k - 1);
-          if (k == 1 && tid == 0) HC_STAMP(5);
-        }
       }
-      const bool alive = !end && wait_or_flag(&sh.tma_full[s], (k / NS) & 1, ws, abort);
+      if (INPLACE && k >= 1 && !end) {
+        // the tile packed over the fp32 stage has to leave before the next fp32 tile can come in
+        compute_barrier();  // every thread has packed tile k-1
+        drain_to(k);
+        mbar_arrive(&sh.stage_free[0]);
+      }
+      const bool alive = !end && wait_or_flag(&sh.tma_full[s], (k / NS) & 1, ws, abort, kSiteComputeTile);
+      if (tid == 0) HC_PH(2);
       if (k == 0 && tid == 0) HC_STAMP(2);
       const uint32_t tile = alive ? sh.tile[slot] : kNoTile;
       if (tile == kNoTile) {
-        if (!kHasIn && k >= 1) {
-          compute_barrier();  // no scan barrier this turn: wait until every thread has packed
-          move_out(k - 1);
-          if (k == 1 && tid == 0) HC_STAMP(5);
+        // end of work: everything still in the ring leaves, then the scanner hears of the end through
+        // the same barrier as of a tile
+        compute_barrier();  // every thread has packed the last tile
+        drain_to(k);
+        if (INPLACE && k >= 1) mbar_arrive(&sh.stage_free[0]);  // the loader's last hand-over waits for it
+        compute_barrier();  // every thread's stores are issued before the scanner announces them
+        if (tid == 0) {
+          sh.stored_upto = k;
+          sh.out_tile[r] = kNoTile;
+          mbar_arrive(&sh.scan_done[r]);
         }
-        compute_barrier();  // every thread's stores of the last tile are issued before the scanner hears of the end
-        if (tid == 0) mbar_arrive(&sh.scan_done[s]);  // wakes the scanner, which sees the end marker too
         break;
       }
       const Seg v = seg_of(tile);
@@ -505,6 +578,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
         } else {
           load_row_global((const uint32_t*)p.local[v.g], v.n_local, row, w);
         }
+        if (!INPLACE) mbar_arrive(&sh.stage_free[s]);  // this thread's row is in registers
         if (OP == kOpAddI32) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) d[i] += (int32_t)w[i];
@@ -517,21 +591,60 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) d[i] += dl[i];
         }
+      } else if (!INPLACE) {
+        mbar_arrive(&sh.stage_free[s]);
       }
 
       // ---- encode ----------------------------------------------------------------------------------
+      if (tid == 0) HC_PH(3);
       uint32_t A[32];
       BlockCode code = analyse_block<MODE>(d, A);
       uint32_t tot;
-      // the barrier inside the scan also separates the last read of the fp32 tile from the first
-      // write of the packed payload into the same stage
+      if (tid == 0) {
+        HC_PH(4);
+        // which of the packed tiles have their look-back result by now (no waiting); everybody reads
+        // the answer behind the barrier of the scan, so all threads copy the same tiles this turn
+        uint32_t n = copied;
+        while (n < k && mbar_try_wait(&sh.base_ready[n % kRing], (n / kRing) & 1)) ++n;
+        sh.copy_upto[k & 1] = n;
+      }
+      // the barrier inside the scan also orders: the packing of tile k-1 before its copy-out below, the
+      // stores of earlier turns before `stored_upto` is seen by the scanner, and (in place) the last
+      // read of the fp32 tile before the first write of the packed payload over it
       const uint32_t rel = compute_exclusive_scan(code.len, sh.wsum[k & 1], &tot);
+      if (tid == 0) HC_PH(8);
+      uint32_t upto = sh.copy_upto[k & 1];
+      // ring bytes of this tile: [start, end), 16-byte aligned, never across the end of the ring;
+      // every compute thread does the same arithmetic.  `dep` is the newest earlier tile that must
+      // have left first: one whose bytes overlap, or the one kRing - 1 tiles back (slots of the
+      // per-tile words and barriers).
+      uint32_t start = head, end_b = head + ((tot + 15u) & ~15u) + 16u;
+      if (INPLACE || end_b > kRingBytes) {
+        start = 0;
+        end_b = ((tot + 15u) & ~15u) + 16u;
+      }
+      head = end_b;
+      int dep = (int)k - (kRing - 1);
+      if (!INPLACE) {
+#pragma unroll
+        for (int back = 1; back < kRing - 1; ++back) {
+          const int j = (int)k - back;
+          if (j > dep && j >= 0 && sh.ring_start[j % kRing] < end_b && start < sh.ring_end[j % kRing]) dep = j;
+        }
+      }
       if (tid == 0) {
         // publish the tile aggregate right away: successors can look back through this tile
         if (v.lt != 0)
           st_relaxed_gpu_u64(ws.st_out + (size_t)v.g * p.tiles_per_seg + v.lt, st_pack(kStAgg, ws.epoch, tot));
-        sh.out_tot[s] = tot;
-        mbar_arrive(&sh.scan_done[s]);
+        // every thread is past this turn's barrier, so its stores of the tiles copied in earlier turns
+        // are issued: the scanner may announce them (it reads this after the arrival below)
+        sh.stored_upto = copied;
+        // slot r was last used kRing tiles ago, by a tile that left the ring at least a turn ago
+        sh.out_tile[r] = tile;
+        sh.out_tot[r] = tot;
+        sh.ring_start[r] = start;
+        sh.ring_end[r] = end_b;
+        mbar_arrive(&sh.scan_done[r]);
         if (k == 0) HC_STAMP(3);
       }
       // rate bytes (section A) go straight to every destination; a segment shorter than the longest
@@ -545,10 +658,20 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       int W = plane_width(code.rate & 31u);
       W = __reduce_max_sync(0xffffffffu, W);
       transpose_forward(A, W);
-      write_payload(stage_s, rel, code, A, W);
-      if (!kHasIn && k >= 1) {
-        move_out(k - 1);  // packed before this turn's scan barrier
-        if (k == 1 && tid == 0) HC_STAMP(5);
+      if (tid == 0) HC_PH(9);
+      if (!INPLACE) {
+        // packed tiles whose offset is known leave now; the ones this tile needs the room of leave
+        // whatever their look-back takes
+        const bool overlap_now = dep >= (int)copied;  // a tile this one is packed over leaves in this turn
+        if (dep >= (int)upto) upto = (uint32_t)dep + 1u;
+        drain_to(upto);
+        if (tid == 0) HC_PH(6);
+        if (overlap_now) compute_barrier();  // nobody still reads the bytes that this tile is packed over
+      }
+      write_payload(ring + start, rel, code, A, W);
+      if (tid == 0) {
+        HC_PH(7);
+        HC_PH_COUNT();
       }
     }
   }
@@ -630,7 +753,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
       const int s = k & 1;
       if (tile == kNoTile) {
         // end marker; the buffer's previous phase must have been consumed before it is re-armed
-        if (k >= 2) wait_or_flag(&sh.in_free[s], ((k >> 1) - 1) & 1, ws, abort);
+        if (k >= 2) wait_or_flag(&sh.in_free[s], ((k >> 1) - 1) & 1, ws, abort, kSiteDecodeInFree);
         if (lane == 0) sh.tile[k & 3] = kNoTile;
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh.in_full[s]);
@@ -664,9 +787,11 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
     if (lane == 0) HC_STAMP(6);
   } else {
     // ================================ compute warps ==============================================
+    if (tid == 0) HC_PH_START();
     for (uint32_t k = 0;; ++k) {
       const int s = k & 1;
-      bool alive = wait_or_flag(&sh.in_full[s], (k >> 1) & 1, ws, abort);
+      bool alive = wait_or_flag(&sh.in_full[s], (k >> 1) & 1, ws, abort, kSiteDecodeInFull);
+      if (tid == 0) HC_PH(0);
       if (k == 0 && tid == 0) HC_STAMP(2);
       const uint32_t tile = alive ? sh.tile[k & 3] : kNoTile;
       if (tile == kNoTile) break;
@@ -686,6 +811,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
         for (int i = 0; i < 32; ++i) d[i] = 0;
       }
       mbar_arrive(&sh.in_free[s]);
+      if (tid == 0) HC_PH(1);
       if (k == 0 && tid == 0) HC_STAMP(3);
       uint32_t w[32];
 #pragma unroll
@@ -694,14 +820,18 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
       const uint64_t row = (uint64_t)lt * kTileBlocks + tid;
       const bool ragged = row * kBlock < seg.n && (row + 1) * kBlock > seg.n;
       // the TMA store of the previous tile must have finished reading obuf
+      if (tid == 0) HC_PH(2);
       if (tid == 0) tma_wait_group_read<0>();
       compute_barrier();
+      if (tid == 0) HC_PH(3);
       if (tma) {
         store_row_swizzled(obuf, tid, w);
         fence_proxy_async();
       }
       compute_barrier();
       if (tid == 0) {
+        HC_PH(4);
+        HC_PH_COUNT();
         if (tma && (uint64_t)lt * kTileBlocks < full_rows)
           tma_store_2d(&tmaps.m[sg], 0, (int)(lt * kTileBlocks), obuf);
         tma_commit_group();
@@ -718,6 +848,76 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
   }
   if (lane == 0) HC_STAMP_MAX(7);
   cta_epilogue(ws.tick);
+}
+
+// Pre-pass for the stand-alone stream consumers (decompress and the homomorphic adds on streams that
+// no collective step has flagged): reads the rate bytes of up to kMaxIn streams and writes, for every
+// tile, the byte offset of its payload in the arrival-flag format (dev::flag_pack(tag, offset)), so
+// that the consuming kernel stages each tile straight from its flag word instead of walking a
+// look-back chain over the input tile by tile.  One CTA covers kOffTiles tiles of one stream: each
+// warp sums the payload lengths of 32 tiles (lane j ends up with tile j's total), the CTA scans its
+// totals, warp 0 chains the CTA totals with the two-level look-back, then every thread publishes one
+// flag word.  A 256 MB input has 2 MiB of rate bytes and 64 CTAs here: a few microseconds.
+constexpr int kOffThreads = 256;
+constexpr int kOffTiles = kOffThreads;  // tiles per CTA, one flag word per thread
+__global__ void __launch_bounds__(kOffThreads) hc_offsets_kernel(const OffsetParams p) {
+  __shared__ uint32_t s_wsum[kOffThreads / 32];
+  __shared__ uint64_t s_base;
+  __shared__ uint32_t s_ok;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t q = blockIdx.y, cta = blockIdx.x;
+  const uint8_t* in = p.in[q];
+  const uint64_t in_size = p.in_size[q];
+  if (tid == 0) launch_dependents();  // the consumer may fill the SMs right away; it waits on the flags
+  const uint32_t t0 = cta * kOffTiles + warp * 32;
+  uint32_t mine = 0;
+#pragma unroll 8
+  for (int j = 0; j < 32; ++j) {
+    const uint32_t t = t0 + j;
+    uint32_t sum = 0;
+    if (t < p.tiles_per_seg) {
+      const uint64_t b0 = (uint64_t)t * kTileBlocks + (uint64_t)lane * 4;
+      uint32_t r4 = 0;
+      if (b0 + 4 <= in_size && (reinterpret_cast<uintptr_t>(in) & 3u) == 0) {
+        r4 = __ldcg(reinterpret_cast<const uint32_t*>(in + b0));
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (b0 + k < in_size) r4 |= ld_cg_u8(in + b0 + k) << (8 * k);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) sum += payload_len((r4 >> (8 * k)) & 0xffu);
+    }
+    sum = __reduce_add_sync(0xffffffffu, sum);
+    if (lane == j) mine = sum;
+  }
+  const uint32_t inc = warp_inclusive_scan(mine, lane);
+  if (lane == 31) s_wsum[warp] = inc;
+  __syncthreads();
+  uint32_t pre = 0, tot = 0;
+#pragma unroll
+  for (int w = 0; w < kOffThreads / 32; ++w) {
+    const uint32_t v = s_wsum[w];
+    if (w < warp) pre += v;
+    tot += v;
+  }
+  if (warp == 0) {
+    const uint32_t n_cta = (p.tiles_per_seg + kOffTiles - 1) / kOffTiles;
+    const uint32_t stride = n_cta + n_cta / 32 + 4;  // CTA words, then the words of their groups of 32
+    const Chain chain{p.ws.grp_a + (size_t)q * stride, p.ws.grp_a + (size_t)q * stride + n_cta + 1};
+    bool ok = true;
+    const uint64_t excl = lookback(chain, cta, p.ws.epoch, tot, p.ws.spin_limit_ns, p.ws.ctrl + 2, &ok);
+    if (lane == 0) {
+      s_base = p.nrate + excl;
+      s_ok = ok ? 1u : 0u;
+    }
+  }
+  __syncthreads();
+  const uint32_t t = cta * kOffTiles + tid;
+  if (t < p.tiles_per_seg) {
+    const uint64_t off = s_ok ? s_base + pre + (inc - mine) : kFlagOffsetMask;
+    st_relaxed_sys_u64(p.flags[q] + t, flag_pack(p.tag, off));
+  }
 }
 
 // fp32 -> int32 Lorenzo deltas of the quantised values, padded with zero deltas to whole blocks.
@@ -821,7 +1021,9 @@ DeviceInfo& device_info() {
   return d;
 }
 
-constexpr int enc_smem_bytes(int op, int ns) { return dev::enc_smem_base(ns) + (op == kOpCompress ? 0 : 2 * kBufBytes) + 1024; }
+constexpr int enc_smem_bytes(int op, int ns, bool inplace) {
+  return dev::enc_cbuf_off(op, ns, inplace) + (op == kOpCompress ? 0 : 2 * kBufBytes) + 1024;
+}
 constexpr int kDecSmem = kTileBytes + 2 * kBufBytes + 1024;
 
 template <typename K>
@@ -848,43 +1050,59 @@ cudaError_t launch_overlapped(void (*kernel)(Params...), int grid, int block, in
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
-template <int OP, int MODE, int NS = dev::enc_stages(OP)>
-cudaError_t launch_encode_t(const TensorMaps& map, const EncParams& p, int grid, cudaStream_t stream, bool overlap) {
-  constexpr int smem = enc_smem_bytes(OP, NS);
-  static thread_local bool attr_done[64] = {};
+// CTAs of `kernel` that one GPU holds at the same time, asked of the runtime once per device.  The
+// kernels are written for a grid that is resident as a whole (CTA i owns tile i, and every look-back
+// waits for tiles held by other CTAs of the grid), so the grid is cut to this number, never assumed.
+template <typename K>
+int resident_ctas(K kernel, int threads, int smem, int* cache) {
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!attr_done[dev & 63]) {
-    cudaError_t e = set_smem(dev::hc_encode_kernel<OP, MODE, NS>, smem);
-    if (e != cudaSuccess) return e;
-    attr_done[dev & 63] = true;
+  int& c = cache[dev & 63];
+  if (c == 0) {
+    if (set_smem(kernel, smem) != cudaSuccess) return 0;
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, (size_t)smem) != cudaSuccess) return 0;
+    c = per_sm * device_info().sms;
   }
-  if (overlap) return launch_overlapped(dev::hc_encode_kernel<OP, MODE, NS>, grid, dev::kEncThreads, smem, stream, map, p);
-  dev::hc_encode_kernel<OP, MODE, NS><<<grid, dev::kEncThreads, smem, stream>>>(map, p);
+  return c;
+}
+
+template <int OP, int MODE, bool INPLACE = false>
+int encode_capacity() {
+  constexpr int NS = INPLACE ? 1 : dev::enc_stages(OP);
+  static thread_local int cache[64] = {};
+  return resident_ctas(dev::hc_encode_kernel<OP, MODE, NS, INPLACE>, dev::kEncThreads, enc_smem_bytes(OP, NS, INPLACE), cache);
+}
+
+template <int OP, int MODE, bool INPLACE = false>
+cudaError_t launch_encode_t(const TensorMaps& map, const EncParams& p, cudaStream_t stream, bool overlap) {
+  constexpr int NS = INPLACE ? 1 : dev::enc_stages(OP);
+  constexpr int smem = enc_smem_bytes(OP, NS, INPLACE);
+  const int cap = encode_capacity<OP, MODE, INPLACE>();
+  if (cap <= 0) return cudaErrorLaunchOutOfResources;
+  const int grid = (int)(p.n_tiles < (uint32_t)cap ? p.n_tiles : (uint32_t)cap);
+  if (overlap)
+    return launch_overlapped(dev::hc_encode_kernel<OP, MODE, NS, INPLACE>, grid, dev::kEncThreads, smem, stream, map, p);
+  dev::hc_encode_kernel<OP, MODE, NS, INPLACE><<<grid, dev::kEncThreads, smem, stream>>>(map, p);
   return cudaGetLastError();
 }
 
 template <int OP>
-cudaError_t launch_encode_m(int mode, const TensorMaps& map, const EncParams& p, int grid, cudaStream_t stream,
-                            bool overlap) {
+cudaError_t launch_encode_m(int mode, const TensorMaps& map, const EncParams& p, cudaStream_t stream, bool overlap) {
   switch (mode) {
-    case kModeOutlier: return launch_encode_t<OP, kModeOutlier>(map, p, grid, stream, overlap);
-    case kModePlain: return launch_encode_t<OP, kModePlain>(map, p, grid, stream, overlap);
-    case kModeVec: return launch_encode_t<OP, kModeVec>(map, p, grid, stream, overlap);
+    case kModeOutlier: return launch_encode_t<OP, kModeOutlier>(map, p, stream, overlap);
+    case kModePlain: return launch_encode_t<OP, kModePlain>(map, p, stream, overlap);
+    case kModeVec: return launch_encode_t<OP, kModeVec>(map, p, stream, overlap);
     default: return cudaErrorInvalidValue;
   }
 }
 
 template <int MODE>
-cudaError_t launch_decode_t(const TensorMaps& maps, const DecParams& p, int grid, cudaStream_t stream, bool overlap) {
-  static thread_local bool attr_done[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!attr_done[dev & 63]) {
-    cudaError_t e = set_smem(dev::hc_decode_kernel<MODE>, kDecSmem);
-    if (e != cudaSuccess) return e;
-    attr_done[dev & 63] = true;
-  }
+cudaError_t launch_decode_t(const TensorMaps& maps, const DecParams& p, cudaStream_t stream, bool overlap) {
+  static thread_local int cache[64] = {};
+  const int cap = resident_ctas(dev::hc_decode_kernel<MODE>, dev::kDecThreads, kDecSmem, cache);
+  if (cap <= 0) return cudaErrorLaunchOutOfResources;
+  const int grid = (int)(p.n_tiles < (uint32_t)cap ? p.n_tiles : (uint32_t)cap);
   if (overlap) return launch_overlapped(dev::hc_decode_kernel<MODE>, grid, dev::kDecThreads, kDecSmem, stream, maps, p);
   dev::hc_decode_kernel<MODE><<<grid, dev::kDecThreads, kDecSmem, stream>>>(maps, p);
   return cudaGetLastError();
@@ -925,11 +1143,7 @@ Workspace workspace_view(void* mem, size_t max_elems, uint32_t epoch, uint64_t s
   return w;
 }
 
-int grid_for_tiles(uint32_t n_tiles, int ctas_per_sm) {
-  int cap = device_info().sms * ctas_per_sm;
-  if (cap <= 0) cap = 148 * ctas_per_sm;
-  return (int)(n_tiles < (uint32_t)cap ? n_tiles : (uint32_t)cap);
-}
+int device_sm_count() { return device_info().sms > 0 ? device_info().sms : 148; }
 
 cudaError_t launch_encode(int op, int mode, EncParams p, cudaStream_t stream, bool overlap) {
   if (p.n_seg == 0 || p.n_seg > (uint32_t)kMaxDst || p.n_in > (uint32_t)kMaxIn) return cudaErrorInvalidValue;
@@ -950,19 +1164,21 @@ cudaError_t launch_encode(int op, int mode, EncParams p, cudaStream_t stream, bo
       p.use_tma[g] = make_rows_map(&maps.m[g], p.local[g], rows) ? 1u : 0u;
     }
   }
-  int grid = grid_for_tiles(p.n_tiles, op == kOpCompress ? 4 : 3);
   if (op == kOpAddF32 && mode == kModeOutlier) {
-    // a fourth CTA per SM when that saves a whole round of tiles (tiles per CTA, rounded up)
-    const int grid4 = grid_for_tiles(p.n_tiles, 4);
-    const uint32_t rounds3 = (p.n_tiles + grid - 1) / grid, rounds4 = (p.n_tiles + grid4 - 1) / grid4;
-    if (rounds4 < rounds3 && rounds4 <= 2)
-      return launch_encode_t<kOpAddF32, kModeOutlier, 1>(maps, p, grid4, stream, overlap);
+    // the in-place variant holds a fourth CTA per SM: taken when that saves a whole round of tiles
+    // (tiles per CTA, rounded up) and leaves at most two
+    const uint32_t cap3 = (uint32_t)encode_capacity<kOpAddF32, kModeOutlier, false>();
+    const uint32_t cap4 = (uint32_t)encode_capacity<kOpAddF32, kModeOutlier, true>();
+    if (cap3 && cap4) {
+      const uint32_t rounds3 = (p.n_tiles + cap3 - 1) / cap3, rounds4 = (p.n_tiles + cap4 - 1) / cap4;
+      if (rounds4 < rounds3 && rounds4 <= 2) return launch_encode_t<kOpAddF32, kModeOutlier, true>(maps, p, stream, overlap);
+    }
   }
   switch (op) {
-    case kOpCompress: return launch_encode_m<kOpCompress>(mode, maps, p, grid, stream, overlap);
-    case kOpAddF32: return launch_encode_m<kOpAddF32>(mode, maps, p, grid, stream, overlap);
-    case kOpAddI32: return launch_encode_m<kOpAddI32>(mode, maps, p, grid, stream, overlap);
-    case kOpAddStream: return launch_encode_m<kOpAddStream>(mode, maps, p, grid, stream, overlap);
+    case kOpCompress: return launch_encode_m<kOpCompress>(mode, maps, p, stream, overlap);
+    case kOpAddF32: return launch_encode_m<kOpAddF32>(mode, maps, p, stream, overlap);
+    case kOpAddI32: return launch_encode_m<kOpAddI32>(mode, maps, p, stream, overlap);
+    case kOpAddStream: return launch_encode_m<kOpAddStream>(mode, maps, p, stream, overlap);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -978,19 +1194,34 @@ cudaError_t launch_decode(int mode, DecParams p, cudaStream_t stream, bool overl
   memset(&maps, 0, sizeof(maps));
   for (uint32_t i = 0; i < p.n_seg; ++i)
     p.seg[i].use_tma = make_rows_map(&maps.m[i], p.seg[i].out, p.seg[i].n / kBlock) ? 1u : 0u;
-  int grid = grid_for_tiles(p.n_tiles, 4);
   switch (mode) {
     case kModeOutlier:
-    case kModePlain: return launch_decode_t<kModeOutlier>(maps, p, grid, stream, overlap);
-    case kModeVec: return launch_decode_t<kModeVec>(maps, p, grid, stream, overlap);
+    case kModePlain: return launch_decode_t<kModeOutlier>(maps, p, stream, overlap);
+    case kModeVec: return launch_decode_t<kModeVec>(maps, p, stream, overlap);
     default: return cudaErrorInvalidValue;
   }
+}
+
+bool offsets_fit(const Workspace& ws, size_t max_elems, uint32_t n_in, uint32_t tiles_per_seg) {
+  (void)ws;
+  const size_t tiles = workspace_tiles(max_elems);
+  const size_t groups = tiles / 32 + 1 + kMaxDst;
+  const size_t n_cta = (tiles_per_seg + dev::kOffTiles - 1) / dev::kOffTiles;
+  return (size_t)n_in * (n_cta + n_cta / 32 + 4) <= 2 * groups && (size_t)n_in * tiles_per_seg <= 2 * tiles;
+}
+
+cudaError_t launch_offsets(const OffsetParams& p, cudaStream_t stream) {
+  if (p.n_in == 0 || p.n_in > (uint32_t)kMaxIn || p.tiles_per_seg == 0) return cudaErrorInvalidValue;
+  const dim3 grid((p.tiles_per_seg + dev::kOffTiles - 1) / dev::kOffTiles, p.n_in);
+  dev::hc_offsets_kernel<<<grid, dev::kOffThreads, 0, stream>>>(p);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_quant_pred(int mode, const float* x, int32_t* deltas, uint64_t n, float eb, cudaStream_t stream) {
   if (n == 0) return cudaSuccess;
   uint64_t n_padded = num_blocks(n) * kBlock;
-  int grid = (int)((n_padded + 255) / 256 < 148ull * 16 ? (n_padded + 255) / 256 : 148ull * 16);
+  const uint64_t cap = (uint64_t)(device_info().sms > 0 ? device_info().sms : 148) * 16;
+  int grid = (int)((n_padded + 255) / 256 < cap ? (n_padded + 255) / 256 : cap);
   float recip = 0.5f / eb;
   if (mode == kModeVec) dev::hc_quant_pred_kernel<kModeVec><<<grid, 256, 0, stream>>>(x, deltas, n, n_padded, recip);
   else dev::hc_quant_pred_kernel<kModeOutlier><<<grid, 256, 0, stream>>>(x, deltas, n, n_padded, recip);
@@ -1001,15 +1232,31 @@ cudaError_t launch_sum(float* dst, const float* a, const float* b, const float* 
                        cudaStream_t stream) {
   if (n == 0) return cudaSuccess;
   uint64_t want = (n / 4 + 255) / 256 + 1;
-  int grid = (int)(want < 148ull * 8 ? want : 148ull * 8);
+  const uint64_t cap = (uint64_t)(device_info().sms > 0 ? device_info().sms : 148) * 8;
+  int grid = (int)(want < cap ? want : cap);
   dev::hc_sum_kernel<<<grid, 256, 0, stream>>>(dst, a, b, c, d, n);
   return cudaGetLastError();
 }
 
 }  // namespace hc
 
+// CTAs of one launch that the current device holds at once: op 0 compress, 1 fused add, 2 fused add
+// in place (the variant for launches of about one tile per CTA), 3 decode
+extern "C" int hc_resident_ctas(int op) {
+  switch (op) {
+    case 0: return hc::encode_capacity<hc::kOpCompress, hc::kModeOutlier, false>();
+    case 1: return hc::encode_capacity<hc::kOpAddF32, hc::kModeOutlier, false>();
+    case 2: return hc::encode_capacity<hc::kOpAddF32, hc::kModeOutlier, true>();
+    case 3: {
+      static thread_local int cache[64] = {};
+      return hc::resident_ctas(hc::dev::hc_decode_kernel<hc::kModeOutlier>, hc::dev::kDecThreads, hc::kDecSmem, cache);
+    }
+    default: return 0;
+  }
+}
+
 #ifdef HC_TIMELINE
-// copies the stamps of the last four launches (4 x 1024 CTAs x 16 slots) to the host (synchronises) and clears them
+// copies the stamps of the last four launches (4 x 1024 CTAs x 32 slots) to the host (synchronises) and clears them
 extern "C" int hc_debug_timeline(unsigned long long* host) {
   if (cudaDeviceSynchronize() != cudaSuccess) return -1;
   if (cudaMemcpyFromSymbol(host, hc::dev::g_timeline, sizeof(hc::dev::g_timeline)) != cudaSuccess) return -1;

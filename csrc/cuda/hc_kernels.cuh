@@ -118,6 +118,18 @@ struct DecParams {
 struct TensorMaps {
   CUtensorMap m[kMaxDst];
 };
+// Pre-pass that turns the rate bytes of n_in streams (tiles_per_seg tiles each, nrate rate bytes
+// each) into per-tile arrival flags: flags[q][t] = flag_pack(tag, byte offset of tile t's payload).
+struct OffsetParams {
+  const uint8_t* in[kMaxIn];
+  uint64_t in_size[kMaxIn];
+  uint64_t* flags[kMaxIn];
+  uint32_t n_in;
+  uint32_t tiles_per_seg;
+  uint64_t nrate;
+  uint32_t tag;
+  Workspace ws;  // grp_a / grp_b hold the chain of CTA totals
+};
 
 namespace dev {
 
@@ -496,7 +508,11 @@ __device__ __forceinline__ uint64_t lookback(const Chain& ch, uint32_t tile, uin
     const uint64_t word = st_pack(good ? kStInc : kStBad, epoch, excl + agg);
     st_relaxed_gpu_u64(ch.tile_st + tile, word);
     if (pos == 31) st_relaxed_gpu_u64(ch.group_st + grp, word);
-    if (!good) atomicMax((uint32_t*)err_word, (uint32_t)kErrTimeout);
+    if (!good) {
+      // err_word is word 2 of the workspace header; word 3 keeps the first wait that ran out (11: a look-back)
+      if (*err_word < (uint32_t)kErrTimeout) atomicCAS((uint32_t*)err_word + 1, 0u, 11u);
+      atomicMax((uint32_t*)err_word, (uint32_t)kErrTimeout);
+    }
   }
   *ok = good;
   return excl;

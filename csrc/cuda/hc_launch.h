@@ -14,13 +14,18 @@ namespace hc {
 constexpr int kMaxWorkspaceSets = 4;
 size_t workspace_bytes(size_t max_elems, int sets = 1);
 Workspace workspace_view(void* mem, size_t max_elems, uint32_t epoch, uint64_t spin_limit_ns, int sets = 1);
-int grid_for_tiles(uint32_t n_tiles, int ctas_per_sm);
+int device_sm_count();
 
 // `overlap`: programmatic dependent launch: the kernel may start as soon as every CTA of the previous
 // kernel on the stream is running, and fills the SMs as that kernel's CTAs leave.  Only for launches
 // whose inputs are ordered by arrival flags, with a workspace view of their own set.
 cudaError_t launch_encode(int op, int mode, EncParams p, cudaStream_t stream, bool overlap = false);
 cudaError_t launch_decode(int mode, DecParams p, cudaStream_t stream, bool overlap = false);
+// Per-tile payload offsets of stand-alone input streams as arrival flags (see OffsetParams);
+// offsets_fit says whether the workspace of a handle sized for max_elems has room for the flags of
+// n_in streams of tiles_per_seg tiles and for the pre-pass's own chain.
+bool offsets_fit(const Workspace& ws, size_t max_elems, uint32_t n_in, uint32_t tiles_per_seg);
+cudaError_t launch_offsets(const OffsetParams& p, cudaStream_t stream);
 cudaError_t launch_quant_pred(int mode, const float* x, int32_t* deltas, uint64_t n, float eb, cudaStream_t stream);
 cudaError_t launch_sum(float* dst, const float* a, const float* b, const float* c, const float* d, uint64_t n,
                        cudaStream_t stream);

@@ -62,6 +62,8 @@ struct Layout {
 
 }  // namespace
 
+constexpr int kMaxHostPieces = 32;
+
 struct hc_comm {
   int rank = 0, world = 1;
   size_t max_count = 0;
@@ -82,6 +84,11 @@ struct hc_comm {
   cudaEvent_t ev[hc::kMaxDst + 3] = {};
   int n_ev = 0;
   uint64_t spin_limit_ns = 2000ull * 1000 * 1000;
+  // hc_allreduce_host: device staging (created on first use), copy streams, one event pair per piece
+  float* host_in = nullptr;
+  float* host_out = nullptr;
+  cudaStream_t s_h2d = nullptr, s_d2h = nullptr;
+  cudaEvent_t ev_in[kMaxHostPieces] = {}, ev_out[kMaxHostPieces] = {}, ev_fork = nullptr, ev_join = nullptr;
 };
 
 namespace {
@@ -169,6 +176,16 @@ void hc_comm_destroy(hc_comm* c) {
   if (c->ws_mem) cudaFree(c->ws_mem);
   if (c->sizes) cudaFree(c->sizes);
   if (c->host_codec) hc_codec_destroy(c->host_codec);
+  if (c->host_in) cudaFree(c->host_in);
+  if (c->host_out) cudaFree(c->host_out);
+  if (c->s_h2d) cudaStreamDestroy(c->s_h2d);
+  if (c->s_d2h) cudaStreamDestroy(c->s_d2h);
+  for (auto& e : c->ev_in)
+    if (e) cudaEventDestroy(e);
+  for (auto& e : c->ev_out)
+    if (e) cudaEventDestroy(e);
+  if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+  if (c->ev_join) cudaEventDestroy(c->ev_join);
   delete c;
 }
 
@@ -448,6 +465,58 @@ extern "C" int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
                            : allreduce_direct(c, d_sbuf, d_rbuf, count, eb, stream);
 }
 
+// Host buffers in, host buffers out.  The reference's hostptr entry points copy the whole input up,
+// run, and copy the whole output down, one after the other (GSZ_compress_hostptr,
+// HomComp/src/GSZ_entry.cu:28-84).  Here the message is cut into pieces and three streams work as a
+// pipeline: piece i+1 crosses PCIe upwards while piece i is reduced and piece i-1 goes back down,
+// so the call costs about one direction of the PCIe transfer instead of two plus the collective.
+// Every piece is an ordinary hc_allreduce of its own (same partition on all ranks).
+extern "C" int hc_allreduce_host(hc_comm* c, const float* h_sbuf, float* h_rbuf, size_t count, float eb, int pieces,
+                                 hc_stream_t stream) {
+  if (!c || !h_sbuf || !h_rbuf || !(eb > 0.0f) || count > c->max_count) return hc::kErrArgument;
+  if (count == 0) return hc::kOk;
+  if (pieces < 1) pieces = 8;
+  if (pieces > kMaxHostPieces) pieces = kMaxHostPieces;
+  if (!c->host_in) {  // first use: staging buffers, streams and events (set-up, not the call path)
+    const size_t bytes = c->max_count * sizeof(float);
+    if (cudaMalloc(&c->host_in, bytes) != cudaSuccess || cudaMalloc(&c->host_out, bytes) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&c->s_h2d, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&c->s_d2h, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess)
+      return hc::kErrCuda;
+    for (int i = 0; i < kMaxHostPieces; ++i)
+      if (cudaEventCreateWithFlags(&c->ev_in[i], cudaEventDisableTiming) != cudaSuccess ||
+          cudaEventCreateWithFlags(&c->ev_out[i], cudaEventDisableTiming) != cudaSuccess)
+        return hc::kErrCuda;
+  }
+  // pieces of whole tiles for every rank's chunk, the last one takes the remainder
+  const size_t unit = (size_t)hc::kTileElems * (size_t)c->world;
+  size_t piece = (count + (size_t)pieces - 1) / (size_t)pieces;
+  piece = (piece + unit - 1) / unit * unit;
+  // both copy streams start behind everything already on `stream` (an earlier call's kernels still
+  // read the staging input; its copies down still read the staging output, ordered by ev_join)
+  if (cudaEventRecord(c->ev_fork, stream) != cudaSuccess || cudaStreamWaitEvent(c->s_h2d, c->ev_fork, 0) != cudaSuccess ||
+      cudaStreamWaitEvent(c->s_d2h, c->ev_fork, 0) != cudaSuccess)
+    return hc::kErrCuda;
+  int i = 0;
+  for (size_t off = 0; off < count; off += piece, ++i) {
+    const size_t len = count - off < piece ? count - off : piece;
+    if (cudaMemcpyAsync(c->host_in + off, h_sbuf + off, len * sizeof(float), cudaMemcpyHostToDevice, c->s_h2d) !=
+            cudaSuccess ||
+        cudaEventRecord(c->ev_in[i], c->s_h2d) != cudaSuccess || cudaStreamWaitEvent(stream, c->ev_in[i], 0) != cudaSuccess)
+      return hc::kErrCuda;
+    if (int rc = hc_allreduce(c, c->host_in + off, c->host_out + off, len, eb, stream)) return rc;
+    if (cudaEventRecord(c->ev_out[i], stream) != cudaSuccess || cudaStreamWaitEvent(c->s_d2h, c->ev_out[i], 0) != cudaSuccess ||
+        cudaMemcpyAsync(h_rbuf + off, c->host_out + off, len * sizeof(float), cudaMemcpyDeviceToHost, c->s_d2h) != cudaSuccess)
+      return hc::kErrCuda;
+  }
+  // `stream` ends behind the last copy down: synchronising it means the result is on the host
+  if (cudaEventRecord(c->ev_join, c->s_d2h) != cudaSuccess || cudaStreamWaitEvent(stream, c->ev_join, 0) != cudaSuccess)
+    return hc::kErrCuda;
+  return hc::kOk;
+}
+
 extern "C" {
 
 // ---- uncompressed allreduce over the same peer mappings ------------------------------------------
@@ -606,7 +675,7 @@ extern "C" int hc_allreduce_raw(hc_comm* c, const float* d_sbuf, float* d_rbuf, 
   for (int k = 0; k < 3; ++k) p.flag_off[k] = L.raw_flag(k, 0);
   p.ctrl = static_cast<uint32_t*>(c->ws_mem) + 32;  // own counters, apart from the codec's
   p.limit_ns = c->spin_limit_ns;
-  const int grid = 148 * 4;
+  const int grid = hc::device_sm_count() * 4;
   hc_raw_stage_kernel<<<grid, 256, 0, stream>>>(p);
   hc_raw_reduce_kernel<<<grid, 256, 0, stream>>>(p);
   hc_raw_gather_kernel<<<grid, 256, 0, stream>>>(p);

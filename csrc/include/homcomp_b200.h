@@ -69,6 +69,17 @@ void hc_codec_destroy(hc_codec* c);
 int hc_codec_set_timeout_ms(hc_codec* c, unsigned ms);
 // Synchronises the device, returns the sticky hc::Status of the handle and clears it when asked.
 int hc_codec_status(hc_codec* c, int clear);
+// After a status 3 (time-out): which wait ran out FIRST in the launch that failed (call it before
+// clearing the status).  1 loader: fp32 stage not released, 2 loader: input buffer not released,
+// 3 compute: input stream not staged, 4 compute: fp32 tile not landed, 5 compute: no room in the
+// payload ring, 6 scanner: tile total missing, 7 copier: look-back result missing, 8 copier: tile not
+// packed, 9 / 10 the decoder's loader / compute warps, 11 a look-back over tile totals; 0 none.
+int hc_codec_status_site(hc_codec* c);
+// Stand-alone decompress / homomorphic adds on large streams (16 MiB of values and up) first run a
+// small kernel that turns the input's rate bytes into per-tile payload offsets, so the main kernel
+// stages every tile without a look-back over the input (two launches instead of one; on by
+// default).  0 turns it off: one launch, input offsets by decoupled look-back.  Same output bytes.
+int hc_codec_set_prepass(hc_codec* c, int on);
 
 int hc_compress(hc_codec* c, const float* d_x, size_t n, float eb, int mode, uint8_t* d_out, size_t cap,
                 uint64_t* d_size, hc_stream_t stream);
@@ -121,8 +132,16 @@ void hc_comm_destroy(hc_comm* c);
 int hc_comm_set_timeout_ms(hc_comm* c, unsigned ms);
 int hc_comm_status(hc_comm* c, int clear);  // synchronises; sticky hc::Status
 // Sum of `count` floats over all ranks, error at most world * eb per value; d_sbuf and d_rbuf may
-// alias.  Enqueues world + 1 kernels on `stream`; never allocates or synchronises.
+// alias.  Enqueues 3 kernels (direct algorithm, the default) or world + 1 (ring) on `stream`; never
+// allocates or synchronises.
 int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, float eb, hc_stream_t stream);
+// The same sum for buffers in (pinned) host memory: the message crosses PCIe in `pieces` pieces
+// (0 = default 8, at most 32) on two copy streams of the handle while earlier pieces are reduced on
+// `stream` and still earlier ones travel back, so the call costs about one direction of the
+// transfer.  `stream` ends behind the last copy down.  The first call allocates the device staging
+// (2 x max_count floats).  Pageable host memory works but serialises the copies.
+int hc_allreduce_host(hc_comm* c, const float* h_sbuf, float* h_rbuf, size_t count, float eb, int pieces,
+                      hc_stream_t stream);
 // algorithm 0: ring reduce-scatter with one fused kernel per hop (world + 1 launches);
 // algorithm 1 (default): direct scatter -> reduce -> gather for a switched fabric (3 launches).
 // Both produce byte-identical reduced streams, hence bit-identical results.

@@ -247,3 +247,33 @@ def test_stream_files_cross_between_device_and_host(tmp_path):
     assert on_gpu.is_cuda and on_gpu.shape == t.shape
     assert torch.equal(on_gpu.cpu(), on_cpu)
     assert (on_cpu - t).abs().max().item() <= eb * 1.0001
+
+
+@pytest.mark.parametrize("name", ["gradient", "sparse"])
+def test_prepass_offsets_give_the_same_bytes(name):
+    """Streams of 1024 tiles and more get their tile offsets from the pre-pass kernel: decode and all
+    homomorphic adds must give the bytes of the look-back path and of the oracle, ragged tail included."""
+    n, eb = 1024 * 4096 + 4096 * 3 + 77, 1e-4
+    c = ops.Codec(max_elems=2 * n + 65536)  # two input streams, each rounded up to whole chunks
+    x, y = ALL[name](n, seed=11), ALL[name](n, seed=12)
+    sx, sy = ops.cpu_compress(x, eb), ops.cpu_compress(y, eb)
+    gsx = _gpu(np.concatenate([sx, np.zeros(32, np.uint8)]))
+    gsy = _gpu(np.concatenate([sy, np.zeros(32, np.uint8)]))
+    ref_add = ops.cpu_hom_add(sx, y, eb)
+    ref_dec = ops.cpu_decompress(sx, n, eb)
+    for on in (True, False):
+        c.set_prepass(on)
+        d = torch.full((n,), 3.0, device="cuda")
+        c.decompress(gsx, n, eb, out=d, stream_bytes=sx.size)
+        np.testing.assert_array_equal(d.cpu().numpy(), ref_dec)
+        out, size = c.hom_add(gsx, _gpu(y), eb, stream_bytes=sx.size)
+        np.testing.assert_array_equal(_stream(out, size), ref_add)
+        out, size = c.hom_add_streams(gsx, gsy, n, a_bytes=sx.size, b_bytes=sy.size)
+        np.testing.assert_array_equal(_stream(out, size), ref_add)
+        out, size = c.hom_add_multi([gsx, gsy], torch.zeros(n, device="cuda"), eb, stream_bytes=[sx.size, sy.size])
+        np.testing.assert_array_equal(_stream(out, size), ref_add)
+        assert c.status() == 0
+    # a truncated stream is still reported, not read past its end
+    c.set_prepass(True)
+    c.decompress(gsx, n, eb, stream_bytes=sx.size - 5000)
+    assert c.status() == 2

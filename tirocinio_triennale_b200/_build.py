@@ -71,22 +71,25 @@ def build_cpu(force: bool = False) -> Path:
     return lib
 
 
-def build_cuda(force: bool = False, verbose: bool = False) -> Path:
-    lib = LIBDIR / "libhomcomp_b200.so"
+def build_cuda(force: bool = False, verbose: bool = False, timeline: bool = False) -> Path:
+    """``timeline=True`` builds a second library, ``libhomcomp_b200_tl.so``, whose kernels stamp a
+    per-CTA timeline (``-DHC_TIMELINE``; read it with ``utils/timeline.py``).  Slower; never the default."""
+    lib = LIBDIR / ("libhomcomp_b200_tl.so" if timeline else "libhomcomp_b200.so")
     if not (force or _stale(lib)):
         return lib
     nvcc = nvcc_path()
     if nvcc is None:
         raise RuntimeError("nvcc not found; cannot build the sm_100a library")
     LIBDIR.mkdir(parents=True, exist_ok=True)
-    OBJDIR.mkdir(parents=True, exist_ok=True)
+    objdir = OBJDIR / "tl" if timeline else OBJDIR
+    objdir.mkdir(parents=True, exist_ok=True)
     inc = ["-I", str(CSRC / "include"), "-I", str(CSRC / "cuda")]
 
     def compile_one(src: str) -> str:
-        obj = OBJDIR / (Path(src).name + ".o")
+        obj = objdir / (Path(src).name + ".o")
         s = CSRC / src
         if src.endswith(".cu"):
-            extra = ["-Xptxas", "-v"] if verbose else []
+            extra = (["-Xptxas", "-v"] if verbose else []) + (["-DHC_TIMELINE"] if timeline else [])
             out = _run([nvcc, *NVCC_FLAGS, *extra, *inc, "-c", str(s), "-o", str(obj)])
         else:
             out = _run(["g++", *CXX_FLAGS, *inc, "-c", str(s), "-o", str(obj)])
@@ -126,4 +129,6 @@ def build_cli(force: bool = False):
 if __name__ == "__main__":
     print(build_cpu(force="--force" in sys.argv))
     print(build_cuda(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--timeline" in sys.argv:
+        print(build_cuda(force="--force" in sys.argv, timeline=True))
     print(build_cli(force="--force" in sys.argv))

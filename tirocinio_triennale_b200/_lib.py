@@ -64,6 +64,8 @@ def _declare_cuda(lib):
         "hc_codec_create": [C.POINTER(vp), sz],
         "hc_codec_create_in": [C.POINTER(vp), vp, sz, sz, vp],
         "hc_codec_set_timeout_ms": [vp, C.c_uint],
+        "hc_codec_set_prepass": [vp, i],
+        "hc_codec_status_site": [vp],
         "hc_codec_status": [vp, i],
         "hc_compress": [vp, vp, sz, f, i, vp, sz, vp, vp],
         "hc_decompress": [vp, vp, sz, sz, f, i, vp, vp],
@@ -94,13 +96,18 @@ def cpu():
 
 
 def cuda():
-    """The sm_100a library.  Built on demand when nvcc is present; raises otherwise."""
+    """The sm_100a library.  Built on demand when nvcc is present; raises otherwise.
+    With ``HC_TIMELINE=1`` in the environment the instrumented build is loaded instead
+    (``utils/timeline.py``)."""
     global _cuda
     with _lock:
         if _cuda is None:
-            path = Path(_build.LIBDIR / "libhomcomp_b200.so")
+            import os
+
+            tl = os.environ.get("HC_TIMELINE", "0") not in ("", "0")
+            path = Path(_build.LIBDIR / ("libhomcomp_b200_tl.so" if tl else "libhomcomp_b200.so"))
             if _build.nvcc_path() is not None:
-                path = _build.build_cuda()
+                path = _build.build_cuda(timeline=tl)
             if not path.exists():
                 raise RuntimeError("libhomcomp_b200.so is missing and nvcc is not available to build it")
             lib = C.CDLL(str(path))

@@ -25,6 +25,7 @@ def declare(lib):
         "hc_comm_status": [vp, i],
         "hc_allreduce": [vp, vp, vp, sz, f, vp],
         "hc_allreduce_raw": [vp, vp, vp, sz, vp],
+        "hc_allreduce_host": [vp, vp, vp, sz, f, i, vp],
         "hc_comm_set_trace": [vp, i],
         "hc_comm_set_algorithm": [vp, i],
         "hc_comm_set_overlap": [vp, i],

@@ -51,6 +51,16 @@ class Codec:
     def set_timeout_ms(self, ms: int):
         _lib.check(self.lib.hc_codec_set_timeout_ms(self._h, int(ms)), "set_timeout")
 
+    def status_site(self) -> int:
+        """After a time-out: code of the wait that ran out first (see ``hc_codec_status_site``)."""
+        with torch.cuda.device(self.device):
+            return int(self.lib.hc_codec_status_site(self._h))
+
+    def set_prepass(self, on: bool = True):
+        """Large stand-alone inputs: tile offsets from a small pre-pass kernel (default) or from a
+        look-back inside the consuming kernel (``False``).  Same bytes either way."""
+        _lib.check(self.lib.hc_codec_set_prepass(self._h, 1 if on else 0), "set_prepass")
+
     def status(self, clear: bool = True) -> int:
         """Synchronises and returns the sticky device status (0 = ok)."""
         with torch.cuda.device(self.device):

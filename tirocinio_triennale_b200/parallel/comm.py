@@ -15,10 +15,10 @@ from .. import _lib
 
 
 class CompressedAllreduce:
-    """Handle-based compressed ring allreduce for float32 CUDA tensors of up to ``max_count`` values.
+    """Handle-based compressed allreduce for float32 CUDA tensors of up to ``max_count`` values.
 
-    Every call enqueues ``world + 1`` kernels on the current stream: it never allocates, never
-    synchronises the host and never copies a size to the host.  The result is identical on all
+    Every call enqueues 3 kernels (``"direct"``, the default) or ``world + 1`` (``"ring"``) on the
+    current stream: it never allocates, never synchronises the host and never copies a size to the host.  The result is identical on all
     ranks and equals ``2 * eb * sum_r quantise(x_r)``: the error is at most ``world * eb``.
     """
 
@@ -96,12 +96,33 @@ class CompressedAllreduce:
         if recv is None:
             recv = send
         n = send.numel()
-        if n > self.max_count or recv.numel() != n:
-            raise ValueError("tensor larger than the handle's max_count")
+        if n > self.max_count or recv.numel() != n or recv.dtype != torch.float32 or not recv.is_cuda \
+                or not recv.is_contiguous():
+            raise ValueError("recv must be a contiguous float32 CUDA tensor of send's size, at most max_count values")
         with torch.cuda.device(self.device):
             _lib.check(self.lib.hc_allreduce(self._h, send.data_ptr(), recv.data_ptr(), n, eb,
                                              torch.cuda.current_stream().cuda_stream), "allreduce")
         self._last = (n, eb)
+        return recv
+
+    def allreduce_host(self, send: torch.Tensor, recv: torch.Tensor | None = None, eb: float = 1e-4,
+                       pieces: int = 8) -> torch.Tensor:
+        """The same sum for float32 tensors in host memory (pin them: ``.pin_memory()``).  The message
+        crosses PCIe in ``pieces`` pieces while earlier pieces are being reduced and still earlier ones
+        travel back, so a call costs about one direction of the transfer.  Asynchronous: the result is
+        on the host once the current CUDA stream has been synchronised."""
+        if send.dtype != torch.float32 or send.is_cuda or not send.is_contiguous():
+            raise ValueError("expected a contiguous float32 host tensor")
+        if recv is None:
+            recv = send
+        n = send.numel()
+        if n > self.max_count or recv.numel() != n or recv.dtype != torch.float32 or recv.is_cuda \
+                or not recv.is_contiguous():
+            raise ValueError("recv must be a contiguous float32 host tensor of send's size, at most max_count values")
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.hc_allreduce_host(self._h, send.data_ptr(), recv.data_ptr(), n, eb, int(pieces),
+                                                  torch.cuda.current_stream().cuda_stream), "allreduce_host")
+        self._last = (min(n, -(-n // max(1, pieces))), eb)
         return recv
 
     def allreduce_raw(self, send: torch.Tensor, recv: torch.Tensor | None = None) -> torch.Tensor:
@@ -110,6 +131,8 @@ class CompressedAllreduce:
             raise ValueError("expected a contiguous float32 CUDA tensor")
         if recv is None:
             recv = send
+        if recv.numel() != send.numel() or recv.dtype != torch.float32 or not recv.is_cuda or not recv.is_contiguous():
+            raise ValueError("recv must be a contiguous float32 CUDA tensor of send's size")
         with torch.cuda.device(self.device):
             _lib.check(self.lib.hc_allreduce_raw(self._h, send.data_ptr(), recv.data_ptr(), send.numel(),
                                                  torch.cuda.current_stream().cuda_stream), "allreduce_raw")
@@ -164,15 +187,20 @@ class CompressedAllreduce:
             "step_ms": self.last_step_ms(), "status": self.status(clear=clear_status),
         }
 
-    def close(self):
+    def close(self, collective: bool = True):
+        """Releases the handle and the mappings.  ``collective=True`` (the explicit call) first meets the
+        other ranks at a barrier, because nobody may still be storing into a region that is about to go
+        away; the destructor passes ``False`` and only releases local resources: garbage collection
+        runs at different times on different ranks and must never wait for a peer."""
         if self._h is None:
             return
         with torch.cuda.device(self.device):
             torch.cuda.synchronize()
-            try:
-                dist.barrier(group=self.group)  # nobody may still be storing into a region about to go away
-            except Exception:
-                pass
+            if collective:
+                try:
+                    dist.barrier(group=self.group)
+                except Exception:
+                    pass
             self.lib.hc_comm_destroy(self._h)
             self._h = None
             for p in self._peers.values():
@@ -185,6 +213,6 @@ class CompressedAllreduce:
 
     def __del__(self):
         try:
-            self.close()
+            self.close(collective=False)
         except Exception:
             pass

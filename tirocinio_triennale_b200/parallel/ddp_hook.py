@@ -5,8 +5,11 @@ allreduce instead of NCCL.
     ddp_model.register_comm_hook(state, compressed_allreduce_hook)
 
 CUDA buckets run on a side stream (``state.stream``) so the collective of bucket k overlaps the
-backward pass that fills bucket k+1; the returned future completes on that stream without a host
-synchronisation.  fp32 buckets only (the codec is fp32); other dtypes fall back to a plain
+backward pass that fills bucket k+1.  The hook returns a CUDA-aware future whose result is set
+under the side stream: the backward stream is never made to wait, only whoever consumes the bucket
+(DDP's finalisation, through ``Future.wait``) is ordered behind the collective, and the host never
+blocks.  ``state.check()`` reads the sticky device status (time-outs, missing peers) when the
+trainer wants to know.  fp32 buckets only (the codec is fp32); other dtypes fall back to a plain
 allreduce.  CPU buckets (gloo groups) go through the host-rank ring, which keeps the hook testable
 without a GPU.  The reference ships the collective only; a trainer integration is the motivating
 use case of its thesis (section 7.1), not part of its code.
@@ -36,6 +39,16 @@ class CompressedHookState:
             self.stream = torch.cuda.Stream()
         return self._ar
 
+    def check(self):
+        """Synchronises and raises if a collective of this hook reported a device-side error
+        (``kErrTimeout`` / ``kErrPeer`` / ``kErrCapacity``) since the last check."""
+        if self._ar is not None:
+            st = self._ar.status(clear=True)
+            if st != 0:
+                from .. import _lib
+
+                raise _lib.HomCompError(st, "compressed gradient allreduce")
+
     def close(self):
         if self._ar is not None:
             self._ar.close()
@@ -63,17 +76,21 @@ def compressed_allreduce_hook(state: CompressedHookState, bucket: dist.GradBucke
         fut.set_result(buf)
         return fut
 
+    return launch_bucket(state, buf, world)
+
+
+def launch_bucket(state: CompressedHookState, buf: torch.Tensor, world: int) -> torch.futures.Future[torch.Tensor]:
+    """Averages ``buf`` in place over the ranks on ``state.stream`` and returns a CUDA-aware future.
+    The stream that calls this is not blocked: kernels queued on it afterwards run concurrently with
+    the collective."""
     ar = state.engine()
     cur = torch.cuda.current_stream()
     state.stream.wait_stream(cur)  # the bucket's gradients are complete on the backward stream
+    fut = torch.futures.Future(devices=[buf.device])
     with torch.cuda.stream(state.stream):
         ar.allreduce(buf, buf, state.eb)
         buf.div_(world)
         buf.record_stream(state.stream)
-        ev = torch.cuda.Event()
-        ev.record(state.stream)
-    # DDP waits for the future on the host and then uses the bucket on its own stream: order that
-    # stream behind ours instead of blocking the host
-    cur.wait_event(ev)
-    fut.set_result(buf)
+        # records an event on state.stream; Future.wait() / then() order their stream behind it
+        fut.set_result(buf)
     return fut
