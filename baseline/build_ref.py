@@ -6,8 +6,8 @@ but absent, HomComp/src/GSZ_entry.cu:3) and the declaration fix in ``intra_node_
 (HomComp/src/cuda_awareallreduce.cu:648-658: ``send_count`` declared twice, ``recv_count`` never).
 That function is not on the benchmarked path.  One more change is needed to RUN the kernels on
 B200 at all: the shared variable ``excl_sum`` is read uninitialised by the first chunk of every
-kernel (see the comment in ``build``); it is set to 0 here.  ``mpi.h`` comes from baseline/mpi_shim because no
-MPI exists on the image.  Nothing of this library is used by the product.
+kernel (see the comment in ``build``); it is set to 0 here.  ``mpi.h`` comes from csrc/mpi_shim (the single-host MPI of
+this repository) because no MPI exists on the image.  Nothing of this library is used by the product.
 """
 from __future__ import annotations
 
@@ -18,7 +18,10 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-REF = Path(os.environ.get("HC_REFERENCE_ROOT", "/root/reference")) / "HomComp"
+# where the reference checkout lives: HC_REFERENCE_ROOT, the first argument of the command line, or a
+# directory called "reference" beside this repository
+REF = Path(os.environ.get("HC_REFERENCE_ROOT") or (HERE.parent.parent / "reference")) / "HomComp"
+SHIM = HERE.parent / "csrc" / "mpi_shim"
 OUT = HERE / "_ref"
 LIB = OUT / "libhomcomp_ref.so"
 
@@ -59,9 +62,9 @@ def build(force: bool = False) -> Path | None:
         q.write_text(t)
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     cmd = [nvcc, "-std=c++17", "-gencode", "arch=compute_100,code=sm_100", "-O3", "-shared", "-Xcompiler", "-fPIC",
-           "-w", "-I", str(HERE / "mpi_shim"), "-I", str(inc),
+           "-w", "-I", str(SHIM), "-I", str(inc),
            str(src / "GSZ.cu"), str(src / "homcomp.cu"), str(src / "GSZ_entry.cu"), str(src / "cuda_awareallreduce.cu"),
-           str(HERE / "ref_driver.cu"), str(HERE / "mpi_shim" / "mpi_shim.cpp"), "-o", str(LIB), "-lcudart", "-lrt"]
+           str(HERE / "ref_driver.cu"), str(SHIM / "mpi_shim.cpp"), "-o", str(LIB), "-lcudart", "-lrt"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         (OUT / "build.log").write_text(r.stdout + r.stderr)
@@ -74,4 +77,6 @@ def build(force: bool = False) -> Path | None:
 
 
 if __name__ == "__main__":
+    if len(sys.argv) > 1:
+        REF = Path(sys.argv[1]) / "HomComp"
     print(build(force=True))

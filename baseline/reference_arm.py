@@ -109,15 +109,15 @@ def main(args):
         host_in = [torch.empty(COUNT, dtype=torch.float32).pin_memory() for _ in range(NBUF)]
         for b in range(NBUF):
             host_in[b].copy_(xs[b])
-        host_out = torch.empty(1, dtype=torch.float32).pin_memory()
+        host_out = [torch.empty(COUNT, dtype=torch.float32).pin_memory() for _ in range(NBUF)]
 
-        def e2e_step(i):
+        def e2e_step(i):  # the reference has no host-buffer collective: copy up, its call, copy down
             b = i % NBUF
             xs[b].copy_(host_in[b], non_blocking=True)
             step(i)
-            host_out.copy_(outs[b][:1], non_blocking=True)
+            host_out[b].copy_(outs[b], non_blocking=True)
             torch.cuda.current_stream().synchronize()
-            return float(host_out[0])
+            return float(host_out[b][0])
 
         for i in range(3):
             e2e_step(i)
@@ -133,22 +133,22 @@ def main(args):
             "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": value / world / B.PUBLISHED_PER_RANK_GBS,
             "dtype": "fp32 data, int32 quantised domain", "data": "synthetic",
-            "config": {
-                "model": "reference allreduce_ring_comprs_hom_sum_F, 64 MiB float32 per rank, gradient-like"
-                         if world > 1 else
-                         "reference GSZ_compress_deviceptr_outlier + GSZ_decompress_deviceptr_outlier, 64 MiB float32"
-                         " (its allreduce is a no-op for one rank)",
-                "global_batch": COUNT * world, "seq_len": COUNT, "parallelism": "ring%d" % world, "error_bound": EB,
+            "config": B.bench_config(world),
+            "implementation": {
+                "algorithm_timed": "reference allreduce_ring_comprs_hom_sum_F (host-driven ring over MPI point to point)"
+                                   if world > 1 else
+                                   "reference GSZ_compress_deviceptr_outlier + GSZ_decompress_deviceptr_outlier "
+                                   "(its allreduce is a no-op for one rank)",
                 "transport": "single-host MPI shim: IPC-mapped device mailboxes (GPU to GPU copies)",
                 "build": "nvcc -arch sm_100 -O3 of the reference sources; not byte-for-byte unmodified: stand-in "
                          "comprs_test.cuh, declaration fix in intra_node_allgather, and the __shared__ excl_sum "
                          "that the first chunk reads uninitialised is set to 0 (as shipped the kernels store out "
                          "of bounds on B200)",
-                "l2": "rotating %d input and %d output buffers" % (NBUF, NBUF),
+                "e2e_call": "torch copy of the input to the device, the reference's call, torch copy of the result back",
             },
             "per_rank_gbs": value / world, "max_abs_err": max_err, "err_bound_world_x_eb": world * EB,
             "e2e": {"value": total_bytes / (e2e_ms / args.steps * 1e-3) / 1e9, "unit": "GB/s aggregate",
-                    "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": 4 * COUNT, "d2h_bytes_per_step": 4},
+                    "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": 4 * COUNT, "d2h_bytes_per_step": 4 * COUNT},
             "gpu_launches": args.steps * (2 if world == 1 else 2 * world),
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
         }

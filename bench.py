@@ -9,8 +9,11 @@ abs error bound 1e-4) on N B200s of one node.
 Rank 0 prints ONE JSON line.  ``value`` is the job-wide effective bandwidth: N ranks x 64 MiB of
 uncompressed input reduced per call, divided by the device time of the call (CUDA events, max
 over ranks).  ``per_rank_gbs`` is the same time expressed the way the reference's thesis does
-(message bytes / time).  ``e2e`` repeats the measurement through the public Python API with the
-step's input copied from pinned host memory and a 4-byte result read back every step.
+(message bytes / time).  ``e2e`` repeats the measurement through the public host-buffer call
+(``CompressedAllreduce.allreduce_host``): every step the 64 MiB input comes from pinned host memory
+and the 64 MiB result goes back to pinned host memory, the host waiting for it.  Before anything is
+timed one 1 Mi-value call is compared bit for bit with the host oracle (``oracle_bit_exact``);
+``ring_ms_per_step`` is the reference's algorithm (one fused kernel per ring hop) on the same buffers.
 """
 from __future__ import annotations
 
@@ -76,11 +79,45 @@ def timed_loop(fn, steps: int):
     return max_over_ranks(a.elapsed_time(b))
 
 
+def bench_config(world: int) -> dict:
+    """The measured workload, worded identically by both arms (what differs between them is in
+    ``implementation``)."""
+    return {
+        "model": "compressed allreduce of 64 MiB float32 per rank: gradient-like values N(0,0.01) with 1% of the "
+                 "entries x10, per-rank seed, absolute error bound 1e-4 (1 rank: compress + decompress of the buffer)",
+        "global_batch": COUNT * world, "seq_len": COUNT, "parallelism": "allreduce%d" % world, "error_bound": EB,
+        "l2": "rotating %d input and %d output buffers of 64 MiB (%d MiB > 126 MB L2) plus one L2 flush before timing"
+              % (NBUF, NBUF, 2 * NBUF * 64),
+        "e2e": "every step: 64 MiB input from pinned host memory to the device, the allreduce, 64 MiB result back "
+               "to pinned host memory, host waits for it",
+        "vs_baseline_ref": "per-rank GB/s / 0.71 GB/s (thesis Fig 7.2: 32 x A100 + InfiniBand, 64 MB interpolated)",
+    }
+
+
+def oracle_check(ar, rank, world, n=1 << 20):
+    """One small call compared bit for bit with the host oracle (same partition and arithmetic, P host
+    ranks simulated in one process); true only if every rank matches."""
+    import numpy as np
+
+    from tirocinio_triennale_b200 import ops
+    from tirocinio_triennale_b200.utils import datagen
+
+    x = datagen.gradient_like(n, seed=77 + rank, device="cuda")
+    everybody = [torch.empty_like(x) for _ in range(world)]
+    dist.all_gather(everybody, x)
+    want = ops.cpu_ring_allreduce([t.cpu().numpy() for t in everybody], EB)[rank]
+    got = ar.allreduce(x, torch.empty_like(x), EB).cpu().numpy()
+    ok = torch.tensor([1 if np.array_equal(got, want) else 0], device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    return bool(ok.item())
+
+
 def run_ours(args, rank, world, local):
     from tirocinio_triennale_b200.parallel import CompressedAllreduce
     from tirocinio_triennale_b200.utils import datagen, timing
 
     ar = CompressedAllreduce(COUNT)
+    bit_exact = oracle_check(ar, rank, world)
     xs = [datagen.gradient_like(COUNT, seed=1000 * b + rank, device="cuda") for b in range(NBUF)]
     outs = [torch.empty_like(xs[0]) for _ in range(NBUF)]
     flush = timing.L2Flusher()
@@ -88,7 +125,8 @@ def run_ours(args, rank, world, local):
     def step(i):
         ar.allreduce(xs[i % NBUF], outs[i % NBUF], EB)
 
-    for i in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    for i in range(warm):
         step(i)
     flush()
     with timing.ClockSampler(local) as clk:
@@ -104,25 +142,36 @@ def run_ours(args, rank, world, local):
     stream_bytes = ar.last_stream_bytes()
     chunk_bytes = 4 * COUNT / world
     ratio = chunk_bytes / (sum(stream_bytes) / len(stream_bytes))
+    device_result = outs[0].clone()
 
-    # end to end: pinned host input -> device, allreduce, 4-byte result back to the host, every step
+    # the reference's algorithm (ring: one fused kernel per hop) on the same buffers, for comparison
+    ring_ms = None
+    if world > 1:
+        ar.set_algorithm("ring")
+        for i in range(3):
+            step(i)
+        ring_ms = timed_loop(step, args.steps) / args.steps
+        ar.set_algorithm("direct")
+
+    # end to end through the public host-buffer call: pinned host input -> device, allreduce, result ->
+    # pinned host memory, every step, the host waiting for the result
     host_in = [torch.empty(COUNT, dtype=torch.float32).pin_memory() for _ in range(NBUF)]
+    host_out = [torch.empty(COUNT, dtype=torch.float32).pin_memory() for _ in range(NBUF)]
     for b in range(NBUF):
         host_in[b].copy_(xs[b])
-    host_out = torch.empty(1, dtype=torch.float32).pin_memory()
-    dev_in = [torch.empty_like(xs[0]) for _ in range(NBUF)]
 
     def e2e_step(i):
         b = i % NBUF
-        dev_in[b].copy_(host_in[b], non_blocking=True)
-        ar.allreduce(dev_in[b], outs[b], EB)
-        host_out.copy_(outs[b][:1], non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the caller consumes the value every step
-        return float(host_out[0])
+        ar.allreduce_host(host_in[b], host_out[b], EB)
+        torch.cuda.current_stream().synchronize()  # the caller consumes the result every step
+        return float(host_out[b][0])
 
     for i in range(3):
         e2e_step(i)
     e2e_ms = timed_loop(e2e_step, args.steps)
+    e2e_step(0)
+    e2e_same = bool(torch.equal(host_out[0], device_result.cpu()))
+    status = max(status, ar.status())
 
     # uncompressed NCCL allreduce on the same buffers, for context
     ncc = [x.clone() for x in xs]
@@ -140,25 +189,27 @@ def run_ours(args, rank, world, local):
         "metric": "compressed_allreduce_effective_GBps_aggregate",
         "value": value,
         "unit": "GB/s (N ranks x 64 MiB uncompressed input per call / device time, max over ranks)",
-        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": per_step,
+        "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": per_step,
         "higher_is_better": True, "scaling": "weak",
         "vs_baseline": per_rank / PUBLISHED_PER_RANK_GBS,
         "dtype": "fp32 data, int32 quantised domain (no tensor-core stage)", "data": "synthetic",
         "impl": "ours",
-        "config": {
-            "model": "compressed ring allreduce, 64 MiB float32 per rank, N(0,0.01) with 1% x10 outliers, per-rank seed",
-            "global_batch": COUNT * world, "seq_len": COUNT, "parallelism": "allreduce%d (direct scatter-reduce-gather, 3 fused kernels)" % world, "error_bound": EB,
-            "l2": "rotating %d input and %d output buffers (%d MiB > 126 MB L2) plus one L2 flush before timing"
-                  % (NBUF, NBUF, 2 * NBUF * 64),
-            "vs_baseline_ref": "per-rank GB/s / 0.71 GB/s (thesis Fig 7.2: 32 x A100 + InfiniBand, 64 MB interpolated)",
+        "config": bench_config(world),
+        "implementation": {
+            "algorithm_timed": "direct (scatter-compress, fused reduce, decode: 3 kernels per call over peer memory)"
+                               if world > 1 else "compress + decode (2 kernels per call)",
+            "e2e_call": "CompressedAllreduce.allreduce_host: the message crosses PCIe in 8 pieces on two copy streams "
+                        "while earlier pieces are reduced and sent back",
         },
         "per_rank_gbs": per_rank,
+        "ring_ms_per_step": ring_ms,
         "max_abs_err": max_err, "err_bound_world_x_eb": world * EB, "compression_ratio": ratio,
+        "oracle_bit_exact": bit_exact, "e2e_matches_device_path": e2e_same,
         "device_status": status,
         "nccl_uncompressed": {"ms_per_step": nccl_ms / args.steps,
                               "per_rank_gbs": 4.0 * COUNT / (nccl_ms / args.steps * 1e-3) / 1e9},
         "e2e": {"value": total_bytes / (e2e_ms / args.steps * 1e-3) / 1e9, "unit": "GB/s aggregate",
-                "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": 4 * COUNT, "d2h_bytes_per_step": 4},
+                "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": 4 * COUNT, "d2h_bytes_per_step": 4 * COUNT},
         "gpu_launches": args.steps * (3 if world > 1 else 2),  # scatter-compress, reduce, decode per call and rank
         "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
         "hbm_peak_gbs": peaks["hbm_gbs"], "peaks": peaks["source"],

@@ -3,8 +3,10 @@
 // rank holds the same data, so the expected result is world * input; the check is the
 // reference checker's rule |world * in - out| <= 2 eb (world + world / 10)
 // (HomComp/src/utils/checksmooth.c:50-51).  Prints device-timed latency per mode: compressed over
-// peer memory, uncompressed, and host-staged (cpuCopy_* names) with mailboxes between the threads
-// standing in for the host network.
+// peer memory, uncompressed, host-staged (cpuCopy_* names) with mailboxes between the threads
+// standing in for the host network, and, for an even number of GPUs, the hierarchical form
+// (mixed_compressed_allreduce) with the GPUs split into two groups: raw inside a group, compressed
+// between the two.
 //
 //   allreduce_threads [gpus] [count] [eb] [iterations]
 #include <cuda_runtime.h>
@@ -90,7 +92,13 @@ int main(int argc, char** argv) {
   const size_t sym = hc_comm_symmetric_bytes(P, count);
   std::vector<void*> region(P, nullptr);
   std::vector<int> failures(P, 0);
-  std::vector<float> lat_c(P, 0), lat_r(P, 0), lat_h(P, 0);
+  std::vector<float> lat_c(P, 0), lat_r(P, 0), lat_h(P, 0), lat_m(P, 0);
+  // hierarchical mode: two groups of P / 2 ranks; rank r is local rank r % L of group r / L
+  const bool mixed = P >= 2 && P % 2 == 0;
+  const int L = mixed ? P / 2 : P;
+  const size_t slice = hc_chunk_elems(count, L);
+  const size_t sym_local = hc_comm_symmetric_bytes(L, count), sym_inter = hc_comm_symmetric_bytes(2, slice);
+  std::vector<void*> region_local(P, nullptr), region_inter(P, nullptr);
   std::vector<Mailbox> boxes((size_t)P * P);
   Barrier bar(P);
   auto worker = [&](int r) {
@@ -100,10 +108,28 @@ int main(int argc, char** argv) {
       if (q != r) cudaDeviceEnablePeerAccess(q, 0);
     cudaMalloc(&region[r], sym);
     cudaMemset(region[r], 0, sym);
+    if (mixed) {
+      cudaMalloc(&region_local[r], sym_local);
+      cudaMemset(region_local[r], 0, sym_local);
+      cudaMalloc(&region_inter[r], sym_inter);
+      cudaMemset(region_inter[r], 0, sym_inter);
+    }
     cudaDeviceSynchronize();
     bar.wait(sense);
     hc_comm* comm = nullptr;
     if (hc_comm_create(&comm, r, P, count, region.data(), nullptr) != 0) { failures[r] = 1; return; }
+    hc_comm *local = nullptr, *inter = nullptr;
+    if (mixed) {
+      const int g = r / L, l = r % L;
+      std::vector<void*> lb(L), ib(2);
+      for (int q = 0; q < L; ++q) lb[q] = region_local[g * L + q];
+      for (int q = 0; q < 2; ++q) ib[q] = region_inter[q * L + l];
+      if (hc_comm_create(&local, l, L, count, lb.data(), nullptr) != 0 ||
+          hc_comm_create(&inter, g, 2, slice, ib.data(), nullptr) != 0 || hc_comm_set_inter(local, inter) != 0) {
+        failures[r] = 1;
+        return;
+      }
+    }
     Net net{P, r, &boxes};
     hc_host_transport tp{net_send, net_recv, &net};
     if (hc_comm_set_host_transport(comm, &tp) != 0) failures[r] = 1;
@@ -115,49 +141,58 @@ int main(int argc, char** argv) {
     cudaEventCreate(&e0);
     cudaEventCreate(&e1);
     std::vector<float> out(count);
-    for (int mode = 0; mode < 3; ++mode) {
+    for (int mode = 0; mode < (mixed ? 4 : 3); ++mode) {
       float total = 0, ms;
       for (int it = 0; it < iters + 2; ++it) {
         bar.wait(sense);
         cudaEventRecord(e0);
         int rc = mode == 0   ? allreduce_ring_comprs_hom_sum_F(d_in, d_out, count, comm, eb)
                  : mode == 1 ? allreduce_ring_gpu(d_in, d_out, count, comm)
-                             : cpuCopy_allreduce_ring_comprs_hom_sum_F(d_in, d_out, count, comm, eb);
+                 : mode == 2 ? cpuCopy_allreduce_ring_comprs_hom_sum_F(d_in, d_out, count, comm, eb)
+                             : mixed_compressed_allreduce(d_in, d_out, count, local, eb);
         cudaEventRecord(e1);
         cudaEventSynchronize(e1);
         cudaEventElapsedTime(&ms, e0, e1);
         if (rc) failures[r] = 1;
         if (it >= 2) total += ms;
       }
-      (mode == 0 ? lat_c : mode == 1 ? lat_r : lat_h)[r] = total / iters;
+      (mode == 0 ? lat_c : mode == 1 ? lat_r : mode == 2 ? lat_h : lat_m)[r] = total / iters;
       cudaMemcpy(out.data(), d_out, count * 4, cudaMemcpyDeviceToHost);
       const double tol = mode != 1 ? 2.0 * eb * (P + P / 10.0) : 1e-5 * P;
       size_t bad = 0;
       for (size_t i = 0; i < count; ++i)
         if (fabs((double)host[i] * P - out[i]) > tol) ++bad;
       if (bad || hc_comm_status(comm, 1) != 0) failures[r] = 1;
+      if (mode == 3 && (hc_comm_status(local, 1) != 0 || hc_comm_status(inter, 1) != 0)) failures[r] = 1;
       if (bad) fprintf(stderr, "rank %d mode %d: %zu values out of tolerance\n", r, mode, bad);
     }
     bar.wait(sense);
     hc_comm_destroy(comm);
+    if (local) hc_comm_destroy(local);
+    if (inter) hc_comm_destroy(inter);
     cudaFree(d_in);
     cudaFree(d_out);
     bar.wait(sense);
     cudaFree(region[r]);
+    if (mixed) {
+      cudaFree(region_local[r]);
+      cudaFree(region_inter[r]);
+    }
   };
   std::vector<std::thread> th;
   for (int r = 0; r < P; ++r) th.emplace_back(worker, r);
   for (auto& t : th) t.join();
-  float mc = 0, mr = 0, mh = 0;
+  float mc = 0, mr = 0, mh = 0, mm = 0;
   int fail = 0;
   for (int r = 0; r < P; ++r) {
     mc = lat_c[r] > mc ? lat_c[r] : mc;
     mr = lat_r[r] > mr ? lat_r[r] : mr;
     mh = lat_h[r] > mh ? lat_h[r] : mh;
+    mm = lat_m[r] > mm ? lat_m[r] : mm;
     fail |= failures[r];
   }
   printf("gpus %d count %zu eb %g | compressed allreduce %.3f ms (%.1f GB/s) | uncompressed %.3f ms (%.1f GB/s) | "
-         "host-staged %.3f ms | %s\n",
-         P, count, eb, mc, 4e-6 * count / mc, mr, 4e-6 * count / mr, mh, fail ? "FAILED" : "ok");
+         "host-staged %.3f ms | hierarchical (2 groups of %d) %.3f ms | %s\n",
+         P, count, eb, mc, 4e-6 * count / mc, mr, 4e-6 * count / mr, mh, mixed ? L : 0, mm, fail ? "FAILED" : "ok");
   return fail;
 }

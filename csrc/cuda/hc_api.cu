@@ -23,7 +23,7 @@ hc::Workspace next_workspace(hc_codec* c, cudaStream_t stream) {
   c->epoch = (c->epoch + 1) & hc::dev::kEpochMask;
   if (c->epoch == 0) {
     // epoch tags wrapped: forget every old status word (2^22 launches apart)
-    cudaMemsetAsync(static_cast<uint8_t*>(c->ws_mem) + 256, 0, c->ws_bytes - 256, stream);
+    cudaMemsetAsync(static_cast<uint8_t*>(c->ws_mem) + hc::kWorkspaceHeader, 0, c->ws_bytes - hc::kWorkspaceHeader, stream);
     c->epoch = 1;
   }
   return hc::workspace_view(c->ws_mem, c->max_elems, c->epoch, c->spin_limit_ns);

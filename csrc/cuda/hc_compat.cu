@@ -38,9 +38,13 @@ DeviceState* state_for(size_t n) {
   return &s;
 }
 
-void report(const char* what, int rc) {
-  if (rc) fprintf(stderr, "homcomp: %s failed: %s\n", what, hc_status_string(rc));
-}
+// What the caller's output buffer is taken to hold (the reference's signatures carry no capacity):
+// nbEle * 4 bytes as every caller in the reference allocates (HomComp/src/cuda_awareallreduce.cu:191-194),
+// or hc_max_compressed_bytes(nbEle) once the caller has said so.
+int g_capacity_rule = 0;
+size_t assumed_capacity(size_t n) { return g_capacity_rule == 1 ? hc_max_compressed_bytes(n) : n * sizeof(float); }
+
+void report(const char* what, int rc);
 
 void read_size(DeviceState* s, size_t* cmpSize, cudaStream_t stream) {
   uint64_t v = 0;
@@ -52,9 +56,10 @@ void read_size(DeviceState* s, size_t* cmpSize, cudaStream_t stream) {
 void compress_mode(int mode, float* d_x, unsigned char* d_out, size_t n, size_t* cmpSize, float eb, cudaStream_t st) {
   DeviceState* s = state_for(n);
   if (!s) return report("compress", hc::kErrCuda);
-  // the caller's buffer is sized by the caller: the reference assumes nbEle * 4 bytes
-  report("compress", hc_compress(s->codec, d_x, n, eb, mode, d_out, hc_max_compressed_bytes(n), s->d_size, st));
+  cudaMemsetAsync(s->d_size, 0, sizeof(uint64_t), st);  // stays 0 when the stream does not fit
+  report("compress", hc_compress(s->codec, d_x, n, eb, mode, d_out, assumed_capacity(n), s->d_size, st));
   read_size(s, cmpSize, st);
+  report("compress (device)", hc_codec_status(s->codec, 1));
 }
 
 void decompress_mode(int mode, float* d_x, unsigned char* d_in, size_t n, size_t cmpSize, float eb, cudaStream_t st) {
@@ -64,6 +69,17 @@ void decompress_mode(int mode, float* d_x, unsigned char* d_in, size_t n, size_t
 }
 
 }  // namespace
+
+int hc_compat_last_status = 0;
+namespace {
+void report(const char* what, int rc) {
+  if (rc) {
+    hc_compat_last_status = rc;
+    fprintf(stderr, "homcomp: %s failed: %s\n", what, hc_status_string(rc));
+  }
+}
+}  // namespace
+void hc_compat_set_capacity_rule(int rule) { g_capacity_rule = rule == 1 ? 1 : 0; }
 
 void GSZ_compress_deviceptr_plain(float* d, unsigned char* c, size_t n, size_t* sz, float eb, cudaStream_t st) {
   compress_mode(hc::kModePlain, d, c, n, sz, eb, st);
@@ -96,6 +112,7 @@ void GSZ_compress_hostptr(float* oriData, unsigned char* cmpBytes, size_t nbEle,
   cudaMemcpy(d_x, oriData, nbEle * sizeof(float), cudaMemcpyHostToDevice);
   size_t sz = 0;
   compress_mode(hc::kModePlain, d_x, d_c, nbEle, &sz, errorBound, 0);
+  if (sz > assumed_capacity(nbEle)) sz = 0;  // never more than the caller's buffer is taken to hold
   cudaMemcpy(cmpBytes, d_c, sz, cudaMemcpyDeviceToHost);
   if (cmpSize) *cmpSize = sz;
   cudaFree(d_x);
@@ -120,17 +137,21 @@ void homomorphic_sum(unsigned char* d_in, int* d_deltas, unsigned char* d_out, s
   (void)eb;
   DeviceState* s = state_for(n);
   if (!s) return report("homomorphic_sum", hc::kErrCuda);
+  cudaMemsetAsync(s->d_size, 0, sizeof(uint64_t), st);
   report("homomorphic_sum", hc_hom_add_i32(s->codec, d_in, in_size, d_deltas, n, hc::kModeOutlier, d_out,
-                                           hc_max_compressed_bytes(n), s->d_size, st));
+                                           assumed_capacity(n), s->d_size, st));
   read_size(s, cmpSize, st);
+  report("homomorphic_sum (device)", hc_codec_status(s->codec, 1));
 }
 void homomorphic_sum_F(unsigned char* d_in, float* d_local, unsigned char* d_out, size_t n, float eb, size_t* cmpSize,
                        size_t in_size, cudaStream_t st) {
   DeviceState* s = state_for(n);
   if (!s) return report("homomorphic_sum_F", hc::kErrCuda);
+  cudaMemsetAsync(s->d_size, 0, sizeof(uint64_t), st);
   report("homomorphic_sum_F", hc_hom_add_f32(s->codec, d_in, in_size, d_local, n, eb, hc::kModeOutlier, d_out,
-                                             hc_max_compressed_bytes(n), s->d_size, st));
+                                             assumed_capacity(n), s->d_size, st));
   read_size(s, cmpSize, st);
+  report("homomorphic_sum_F (device)", hc_codec_status(s->codec, 1));
 }
 void quant_prediction(const float* d_x, int* d_deltas, float eb, size_t n, cudaStream_t st) {
   report("quant_prediction", hc_quant_pred(d_x, n, eb, hc::kModeOutlier, d_deltas, st));
@@ -154,11 +175,14 @@ int allreduce_ring_comprs_hom_sum_F_seg(const float* s, float* r, size_t c, MPI_
 int allreduce_ring_comprs_hom_sum_F_opt(const float* s, float* r, size_t c, MPI_Comm comm, float eb) {
   return allreduce_ring_comprs_hom_sum_F(s, r, c, comm, eb);
 }
-// one NVSwitch node: the hierarchical allreduce has no inter-node phase left, the intra-node phases
-// are the uncompressed two-shot kernels
+// Hierarchical allreduce: `comm` spans the ranks of one group (the reference takes the ranks that share
+// a node, HomComp/src/cuda_awareallreduce.cu:678-683); the communicator of the ranks with the same
+// local index in the other groups is attached to it with hc_comm_set_inter.  Raw fp32 reduce-scatter
+// inside the group, compressed allreduce (error bound eb) of this rank's slice between the groups, raw
+// all-gather inside the group.  Without an attached communicator there is one group and nothing is
+// compressed, as in the reference when every rank shares a node.
 int mixed_compressed_allreduce(float* s, float* r, size_t count, MPI_Comm comm, float eb) {
-  (void)eb;
-  return hc_allreduce_raw(comm, s, r, count, 0);
+  return hc_allreduce_mixed(comm, hc_comm_get_inter(comm), s, r, count, eb, 0);
 }
 int allreduce_ring_gpu(const float* s, float* r, size_t count, MPI_Comm comm) { return hc_allreduce_raw(comm, s, r, count, 0); }
 

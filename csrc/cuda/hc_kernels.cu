@@ -93,8 +93,10 @@ __device__ __forceinline__ unsigned long long timeline_now() {
 #endif
 
 // the last CTA to leave re-arms the ticket counter for the next launch
-__device__ __forceinline__ void cta_epilogue(uint32_t* tick) {
+// (returns true in thread 0 of that CTA)
+__device__ __forceinline__ bool cta_epilogue(uint32_t* tick) {
   __syncthreads();
+  bool last = false;
   if (threadIdx.x == 0) {
     __threadfence();
     uint32_t done = atomicAdd(tick + 1, 1u);
@@ -102,8 +104,10 @@ __device__ __forceinline__ void cta_epilogue(uint32_t* tick) {
       tick[0] = 0;
       tick[1] = 0;
       __threadfence();
+      last = true;
     }
   }
+  return last;
 }
 
 // bounded mbarrier wait that records a timeout
@@ -162,7 +166,7 @@ __device__ __forceinline__ void loader_stage_stream(const uint8_t* in, uint64_t 
   uint64_t base = base_given;
   if (!base_known) base = nrate + lookback(st, tile, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
   ok = ok && usable;
-  if (ok && base + tot > in_size) {  // stream shorter than its rate bytes imply
+  if (ok && tot && base + tot > in_size) {  // stream shorter than its rate bytes imply
     if (lane == 0) note_error(ws.ctrl, kErrTruncated);
     ok = false;
   }
@@ -267,8 +271,10 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
   };
   auto seg_of = [&](uint32_t tile) -> Seg {
     Seg v;
-    v.g = p.n_seg > 1 ? tile / p.tiles_per_seg : 0u;
-    v.lt = tile - v.g * p.tiles_per_seg;
+    // tickets go round the segments (ticket t: tile t / n_seg of segment t % n_seg), so that all the
+    // streams of a launch grow at the same pace and their consumers can start on every one of them early
+    v.lt = p.n_seg > 1 ? tile / p.n_seg : tile;
+    v.g = p.n_seg > 1 ? tile - v.lt * p.n_seg : 0u;
     v.n = p.n[v.g];
     v.nrate = rate_bytes(v.n);
     v.full_rows = OP == kOpAddI32 ? num_blocks(v.n) : v.n / kBlock;
@@ -452,17 +458,29 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       const uint32_t tile = sh.out_tile[r];
       const uint32_t stored = *((volatile uint32_t*)&sh.stored_upto);  // written before scan_done was raised
       if (tile == kNoTile) {
+        if (lane == 0) HC_STAMP(13);
         raise_flags(stored);  // the compute warps have stored every tile before they send the end marker
+        if (lane == 0) HC_STAMP(9);
         break;
       }
       const Seg v = seg_of(tile);
       const uint32_t tot = sh.out_tot[r];
       bool ok = true;
-      const Chain chain{ws.st_out + (size_t)v.g * p.tiles_per_seg, ws.grp_out + (size_t)v.g * groups_per_seg};
-      const uint64_t excl = lookback(chain, v.lt, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
+      uint64_t excl;
+      if (p.sparse) {
+        // transport buffer of a collective: every tile at the offset it would have if all blocks
+        // before it were incompressible.  No prefix over other CTAs' tiles, hence no waiting; the
+        // consumer takes the offset from the tile's arrival flag.  Payload bytes are summed for the
+        // statistics and turned into the length of the equivalent compact stream by the last CTA.
+        excl = (uint64_t)v.lt * (uint64_t)(kTileBlocks * kMaxBlockPayload);
+        if (lane == 0 && p.size_out) atomicAdd((unsigned long long*)(ws.size_acc + v.g), (unsigned long long)tot);
+      } else {
+        const Chain chain{ws.st_out + (size_t)v.g * p.tiles_per_seg, ws.grp_out + (size_t)v.g * groups_per_seg};
+        excl = lookback(chain, v.lt, ws.epoch, tot, ws.spin_limit_ns, ws.ctrl + 2, &ok);
+      }
       const uint64_t goff = v.nrate + excl;
       if (k == 0 && lane == 0) HC_STAMP(4);
-      if (ok && goff + tot > p.out_cap) {
+      if (ok && tot && goff + tot > p.out_cap) {  // (a tile without payload stores nothing, wherever it would go)
         if (lane == 0) note_error(ws.ctrl, kErrCapacity);
         ok = false;
       }
@@ -470,7 +488,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
         sh.out_base[r] = goff;
         sh.out_ok[r] = ok ? 1u : 0u;
         mbar_arrive(&sh.base_ready[r]);
-        if (ok && v.lt == p.tiles_per_seg - 1 && p.size_out) p.size_out[v.g] = goff + tot;
+        if (!p.sparse && ok && v.lt == p.tiles_per_seg - 1 && p.size_out) p.size_out[v.g] = goff + tot;
         if (fatal_error(ws.ctrl)) *abort = 1;
         HC_PH(11);
       }
@@ -479,7 +497,8 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
         my_g = v.g;
         my_word = flag_pack(p.ring_epoch, ok ? goff : kFlagOffsetMask);
       }
-      if (stored - flagged >= kFlagBatch) raise_flags(stored);
+      // with sparse tiles this warp has nothing else to do: announce whatever has been stored
+      if (stored - flagged >= (p.sparse ? 1u : kFlagBatch)) raise_flags(stored);
     }
   } else {
     // ================================ compute warps ==============================================
@@ -549,7 +568,9 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
         // end of work: everything still in the ring leaves, then the scanner hears of the end through
         // the same barrier as of a tile
         compute_barrier();  // every thread has packed the last tile
+        if (tid == 0) HC_STAMP(5);
         drain_to(k);
+        if (tid == 0) HC_STAMP(12);
         if (INPLACE && k >= 1) mbar_arrive(&sh.stage_free[0]);  // the loader's last hand-over waits for it
         compute_barrier();  // every thread's stores are issued before the scanner announces them
         if (tid == 0) {
@@ -634,7 +655,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       }
       if (tid == 0) {
         // publish the tile aggregate right away: successors can look back through this tile
-        if (v.lt != 0)
+        if (v.lt != 0 && !p.sparse)
           st_relaxed_gpu_u64(ws.st_out + (size_t)v.g * p.tiles_per_seg + v.lt, st_pack(kStAgg, ws.epoch, tot));
         // every thread is past this turn's barrier, so its stores of the tiles copied in earlier turns
         // are issued: the scanner may announce them (it reads this after the arrival below)
@@ -676,7 +697,13 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
     }
   }
   if (lane == 0) HC_STAMP_MAX(7);
-  cta_epilogue(ws.tick);
+  if (cta_epilogue(ws.tick) && p.sparse && p.size_out) {
+    // every CTA has added its tiles' payload bytes (device-scope atomics, fenced before the exit count)
+    for (uint32_t g = 0; g < p.n_seg; ++g) {
+      p.size_out[g] = rate_bytes(p.n[g]) + ws.size_acc[g];
+      ws.size_acc[g] = 0;
+    }
+  }
 }
 
 struct __align__(16) DecShared {
@@ -736,7 +763,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
     // non-blocking; fw receives the tile's arrival flag word when the segment has flags
     auto try_fetch = [&](uint32_t t, uint32_t (&r)[kRatesPerLane], uint64_t& fw) -> bool {
       if (t == kNoTile) return false;
-      const uint32_t sg = t / p.tiles_per_seg, lt = t - sg * p.tiles_per_seg;
+      const uint32_t lt = t / p.n_seg, sg = t - lt * p.n_seg;  // tickets go round the segments
       const DecSegment& seg = p.seg[sg];
       fw = 0;
       if (seg.in_ready && (fw = flag_peek(seg.in_ready + lt, p.ring_epoch)) == 0) return false;
@@ -761,7 +788,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
       }
       const uint32_t tile_nn = tile_n != kNoTile ? take() : kNoTile;
       have_n = try_fetch(tile_n, rates_n, fw_n);
-      const uint32_t sg = tile / p.tiles_per_seg, lt = tile - sg * p.tiles_per_seg;
+      const uint32_t lt = tile / p.n_seg, sg = tile - lt * p.n_seg;
       const DecSegment& seg = p.seg[sg];
       bool usable = true;
       if (!have) {
@@ -795,7 +822,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
       if (k == 0 && tid == 0) HC_STAMP(2);
       const uint32_t tile = alive ? sh.tile[k & 3] : kNoTile;
       if (tile == kNoTile) break;
-      const uint32_t sg = tile / p.tiles_per_seg, lt = tile - sg * p.tiles_per_seg;
+      const uint32_t lt = tile / p.n_seg, sg = tile - lt * p.n_seg;
       const DecSegment& seg = p.seg[sg];
       const bool tma = seg.use_tma != 0;
       const uint64_t full_rows = seg.n / kBlock;
@@ -1080,7 +1107,8 @@ cudaError_t launch_encode_t(const TensorMaps& map, const EncParams& p, cudaStrea
   constexpr int smem = enc_smem_bytes(OP, NS, INPLACE);
   const int cap = encode_capacity<OP, MODE, INPLACE>();
   if (cap <= 0) return cudaErrorLaunchOutOfResources;
-  const int grid = (int)(p.n_tiles < (uint32_t)cap ? p.n_tiles : (uint32_t)cap);
+  int grid = (int)(p.n_tiles < (uint32_t)cap ? p.n_tiles : (uint32_t)cap);
+  if (p.grid_limit && (int)p.grid_limit < grid) grid = (int)p.grid_limit;
   if (overlap)
     return launch_overlapped(dev::hc_encode_kernel<OP, MODE, NS, INPLACE>, grid, dev::kEncThreads, smem, stream, map, p);
   dev::hc_encode_kernel<OP, MODE, NS, INPLACE><<<grid, dev::kEncThreads, smem, stream>>>(map, p);
@@ -1102,7 +1130,8 @@ cudaError_t launch_decode_t(const TensorMaps& maps, const DecParams& p, cudaStre
   static thread_local int cache[64] = {};
   const int cap = resident_ctas(dev::hc_decode_kernel<MODE>, dev::kDecThreads, kDecSmem, cache);
   if (cap <= 0) return cudaErrorLaunchOutOfResources;
-  const int grid = (int)(p.n_tiles < (uint32_t)cap ? p.n_tiles : (uint32_t)cap);
+  int grid = (int)(p.n_tiles < (uint32_t)cap ? p.n_tiles : (uint32_t)cap);
+  if (p.grid_limit && (int)p.grid_limit < grid) grid = (int)p.grid_limit;
   if (overlap) return launch_overlapped(dev::hc_decode_kernel<MODE>, grid, dev::kDecThreads, kDecSmem, stream, maps, p);
   dev::hc_decode_kernel<MODE><<<grid, dev::kDecThreads, kDecSmem, stream>>>(maps, p);
   return cudaGetLastError();
@@ -1119,7 +1148,7 @@ size_t workspace_bytes(size_t max_elems, int sets) {
   size_t groups = tiles / 32 + 1 + kMaxDst;
   if (sets < 1) sets = 1;
   if (sets > kMaxWorkspaceSets) sets = kMaxWorkspaceSets;
-  return 256 + (size_t)sets * 3 * (tiles + groups) * sizeof(uint64_t);
+  return kWorkspaceHeader + (size_t)sets * 3 * (tiles + groups) * sizeof(uint64_t);
 }
 
 Workspace workspace_view(void* mem, size_t max_elems, uint32_t epoch, uint64_t spin_limit_ns, int sets) {
@@ -1132,7 +1161,8 @@ Workspace workspace_view(void* mem, size_t max_elems, uint32_t epoch, uint64_t s
   if (sets > kMaxWorkspaceSets) sets = kMaxWorkspaceSets;
   const size_t set = epoch % (uint32_t)sets;
   w.tick = w.ctrl + 8 + 2 * set;  // words 8..15 of the header
-  w.st_a = reinterpret_cast<uint64_t*>(b + 256) + set * 3 * (tiles + groups);
+  w.size_acc = reinterpret_cast<uint64_t*>(b + 256) + set * kMaxDst;  // second half of the header
+  w.st_a = reinterpret_cast<uint64_t*>(b + kWorkspaceHeader) + set * 3 * (tiles + groups);
   w.st_b = w.st_a + tiles;
   w.st_out = w.st_b + tiles;
   w.grp_a = w.st_out + tiles;
@@ -1171,7 +1201,8 @@ cudaError_t launch_encode(int op, int mode, EncParams p, cudaStream_t stream, bo
     const uint32_t cap4 = (uint32_t)encode_capacity<kOpAddF32, kModeOutlier, true>();
     if (cap3 && cap4) {
       const uint32_t rounds3 = (p.n_tiles + cap3 - 1) / cap3, rounds4 = (p.n_tiles + cap4 - 1) / cap4;
-      if (rounds4 < rounds3 && rounds4 <= 2) return launch_encode_t<kOpAddF32, kModeOutlier, true>(maps, p, stream, overlap);
+      if (p.variant == 2 || (p.variant == 0 && rounds4 < rounds3 && rounds4 <= 2))
+        return launch_encode_t<kOpAddF32, kModeOutlier, true>(maps, p, stream, overlap);
     }
   }
   switch (op) {

@@ -61,6 +61,7 @@ struct Workspace {
   uint64_t* grp_b;
   uint64_t* grp_out;
   uint32_t* tick;  // [0] tile ticket counter, [1] CTAs that have left; re-armed by the last CTA of a launch
+  uint64_t* size_acc;  // [kMaxDst] payload bytes per segment of a launch with sparse tiles; zeroed by its last CTA
   uint32_t epoch;
   uint64_t spin_limit_ns;
 };
@@ -70,7 +71,7 @@ struct Workspace {
 //   * the output goes either to n_dst destinations that all receive the same stream (n_seg == 1:
 //     a ring step, or the reduced chunk pushed to every rank), or, for compress only, to n_seg
 //     independent streams ("segments": segment g compresses local[g] of n[g] values into out[g]);
-//     segments own tiles_per_seg consecutive tickets and their own look-back chain.
+//     tickets go round the segments, each of which has its own look-back chain.
 constexpr int kMaxIn = kMaxDst;
 struct EncParams {
   const void* local[kMaxDst];  // fp32 values or int32 deltas, per segment
@@ -91,6 +92,10 @@ struct EncParams {
   uint8_t* out_mc;               // n_seg == 1 only: multicast alias of all n_dst destinations (NVLS), or null
   uint64_t out_cap;
   uint64_t* size_out;  // device words receiving the exact stream length of each segment (or null)
+  uint32_t sparse;      // 1: tile t's payload goes to byte rate_bytes + t * 16384 of the output instead of right
+                        //    behind tile t-1's (transport buffers of a collective, read through arrival flags only)
+  uint32_t grid_limit;  // at most this many CTAs (0: as many as the GPU holds), to leave room for a concurrent launch
+  uint32_t variant;     // fused add: 0 launcher's choice, 1 payload ring (3 CTAs per SM), 2 in place (4 per SM)
   Workspace ws;
 };
 
@@ -113,6 +118,7 @@ struct DecParams {
   uint32_t n_tiles;  // n_seg * tiles_per_seg
   uint32_t ring_epoch;
   float eb;
+  uint32_t grid_limit;  // at most this many CTAs (0: as many as the GPU holds)
   Workspace ws;
 };
 struct TensorMaps {

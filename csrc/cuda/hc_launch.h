@@ -12,6 +12,9 @@ namespace hc {
 // `sets` > 1 gives consecutive launches (epoch % sets) their own look-back words and ticket counters,
 // so that a launch may start while its predecessor on the stream is still draining.
 constexpr int kMaxWorkspaceSets = 4;
+// bytes in front of the look-back words: status, ticket counters, raw-allreduce counters (first 256
+// bytes), per-segment payload byte counts of the four sets (second 256 bytes)
+constexpr size_t kWorkspaceHeader = 512;
 size_t workspace_bytes(size_t max_elems, int sets = 1);
 Workspace workspace_view(void* mem, size_t max_elems, uint32_t epoch, uint64_t spin_limit_ns, int sets = 1);
 int device_sm_count();

@@ -32,11 +32,31 @@ int device_scratch(PerDevice** out) {
   return hc::kOk;
 }
 
+// upper bound of every device-side wait of the entry point, in nanoseconds (process-wide)
+unsigned long long g_timeout_ns = 2000ull * 1000 * 1000;
+
 }  // namespace
 
 extern "C" {
 
 size_t hc_noalloc_scratch_bytes(void) { return kScratchBytes; }
+
+int hc_noalloc_set_timeout_ms(unsigned ms) {
+  if (ms == 0) return hc::kErrArgument;
+  g_timeout_ns = (unsigned long long)ms * 1000ull * 1000ull;
+  return hc::kOk;
+}
+
+int hc_noalloc_status(int clear) {
+  PerDevice* d = nullptr;
+  if (int rc = device_scratch(&d)) return rc;
+  uint32_t ctrl[4] = {0, 0, 0, 0};
+  if (cudaDeviceSynchronize() != cudaSuccess) return hc::kErrCuda;
+  if (cudaMemcpy(ctrl, d->scratch, sizeof(ctrl), cudaMemcpyDeviceToHost) != cudaSuccess) return hc::kErrCuda;
+  // status word, first-time-out site and the ticket counters a failed launch may have left behind
+  if (clear && cudaMemset(d->scratch, 0, 64) != cudaSuccess) return hc::kErrCuda;
+  return (int)ctrl[2];
+}
 
 int hc_compress_noalloc(const float* d_x, size_t n, float eb, uint8_t* d_out, size_t cap, uint64_t* d_size,
                         hc_stream_t stream) {
@@ -49,12 +69,16 @@ int hc_compress_noalloc(const float* d_x, size_t n, float eb, uint8_t* d_out, si
     if (d_size && cudaMemsetAsync(d_size, 0, sizeof(uint64_t), stream) != cudaSuccess) return hc::kErrCuda;
     return hc::kOk;
   }
-  // ticket counter, exit counter and the sticky error word must start at zero; the status words
-  // behind them are told apart by the call number (epoch) instead
-  if (cudaMemsetAsync(d->scratch, 0, 16, stream) != cudaSuccess) return hc::kErrCuda;
+  // Nothing is cleared here.  The ticket and exit counters (words 8 and 9 of the array) are put back
+  // to zero by the last CTA of every launch, the look-back words behind the header are told apart by
+  // the call number (epoch), and the status word (word 2) is sticky on purpose: it keeps the first
+  // error until hc_noalloc_status(1) has shown it to the caller, and a time-out left there makes
+  // later calls return without output until then.
   d->epoch = (d->epoch + 1) & hc::dev::kEpochMask;
-  if (d->epoch == 0) {  // call numbers wrapped: drop every old status word
-    if (cudaMemsetAsync(d->scratch, 0, kScratchBytes, stream) != cudaSuccess) return hc::kErrCuda;
+  if (d->epoch == 0) {  // call numbers wrapped: drop every old look-back word (not the header)
+    if (cudaMemsetAsync(static_cast<uint8_t*>(d->scratch) + hc::kWorkspaceHeader, 0, kScratchBytes - hc::kWorkspaceHeader,
+                        stream) != cudaSuccess)
+      return hc::kErrCuda;
     d->epoch = 1;
   }
   hc::EncParams p;
@@ -67,7 +91,7 @@ int hc_compress_noalloc(const float* d_x, size_t n, float eb, uint8_t* d_out, si
   p.out[0] = d_out;
   p.out_cap = cap;
   p.size_out = d_size;
-  p.ws = hc::workspace_view(d->scratch, HC_NOALLOC_MAX_ELEMS, d->epoch, 2000ull * 1000 * 1000);
+  p.ws = hc::workspace_view(d->scratch, HC_NOALLOC_MAX_ELEMS, d->epoch, g_timeout_ns);
   return hc::launch_encode(hc::kOpCompress, hc::kModeOutlier, p, stream) == cudaSuccess ? hc::kOk : hc::kErrCuda;
 }
 

@@ -79,11 +79,18 @@ struct hc_comm {
   int algorithm = 1;              // 0 ring (P + 1 kernels), 1 direct (3 kernels)
   bool trace = false;             // record one CUDA event per step of hc_allreduce
   bool overlap = true;            // direct algorithm: steps 2 and 3 start while their predecessor drains
+  int share_scatter = 0, share_reduce = 0;  // direct algorithm: quarters of the GPU for steps 1 and 2 (0: all of it)
+  int reduce_variant = 0;
+  bool sparse = true;  // tiles at fixed offsets in the transport buffers: no look-back across CTAs in any step
   hc_host_transport host_tp = {nullptr, nullptr, nullptr};  // for the host-staged variant
   hc_codec* host_codec = nullptr;                           // created on its first use
   cudaEvent_t ev[hc::kMaxDst + 3] = {};
   int n_ev = 0;
   uint64_t spin_limit_ns = 2000ull * 1000 * 1000;
+  // hierarchical allreduce: communicator of the ranks with this local index in the other groups, and
+  // the buffer for this rank's slice of the group sum (created on first use)
+  hc_comm* inter = nullptr;
+  float* slice = nullptr;
   // hc_allreduce_host: device staging (created on first use), copy streams, one event pair per piece
   float* host_in = nullptr;
   float* host_out = nullptr;
@@ -105,7 +112,7 @@ struct NvtxRange {
 hc::Workspace next_ws(hc_comm* c, cudaStream_t stream) {
   c->ws_epoch = (c->ws_epoch + 1) & hc::dev::kEpochMask;
   if (c->ws_epoch == 0) {
-    cudaMemsetAsync(static_cast<uint8_t*>(c->ws_mem) + 256, 0, c->ws_bytes - 256, stream);
+    cudaMemsetAsync(static_cast<uint8_t*>(c->ws_mem) + hc::kWorkspaceHeader, 0, c->ws_bytes - hc::kWorkspaceHeader, stream);
     c->ws_epoch = 1;
   }
   return hc::workspace_view(c->ws_mem, c->max_count, c->ws_epoch, c->spin_limit_ns, hc::kMaxWorkspaceSets);
@@ -176,6 +183,7 @@ void hc_comm_destroy(hc_comm* c) {
   if (c->ws_mem) cudaFree(c->ws_mem);
   if (c->sizes) cudaFree(c->sizes);
   if (c->host_codec) hc_codec_destroy(c->host_codec);
+  if (c->slice) cudaFree(c->slice);
   if (c->host_in) cudaFree(c->host_in);
   if (c->host_out) cudaFree(c->host_out);
   if (c->s_h2d) cudaStreamDestroy(c->s_h2d);
@@ -272,6 +280,7 @@ static int allreduce_ring(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t
       }
       if (c->mc && P > 1) p.out_mc = c->mc + L.data_off(slot);  // one multimem store reaches all P copies
     }
+    p.sparse = c->sparse ? 1u : 0u;
     p.ws = next_ws(c, stream);
     if (hc::launch_encode(s == 0 ? hc::kOpCompress : hc::kOpAddF32, hc::kModeOutlier, p, stream) != cudaSuccess)
       return hc::kErrCuda;
@@ -364,6 +373,8 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
     }
     if (p.n_seg) {
       p.n_dst = 1;
+      p.sparse = c->sparse ? 1u : 0u;
+      if (overlap && c->share_scatter) p.grid_limit = (uint32_t)(hc::device_sm_count() * c->share_scatter);
       p.ws = next_ws(c, stream);
       if (hc::launch_encode(hc::kOpCompress, hc::kModeOutlier, p, stream) != cudaSuccess) return hc::kErrCuda;
       launched = true;
@@ -397,6 +408,9 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
       p.out_ready[k] = reinterpret_cast<uint64_t*>(c->peer[dst] + L.flag_off(slot));
     }
     if (c->mc && P > 1) p.out_mc = c->mc + L.data_off(slot);  // one multimem store reaches all P copies
+    if (overlap && launched && c->share_reduce) p.grid_limit = (uint32_t)(hc::device_sm_count() * c->share_reduce);
+    p.variant = (uint32_t)c->reduce_variant;
+    p.sparse = c->sparse ? 1u : 0u;
     p.ws = next_ws(c, stream);
     if (hc::launch_encode(P > 1 ? hc::kOpAddF32 : hc::kOpCompress, hc::kModeOutlier, p, stream, overlap && launched) !=
         cudaSuccess)
@@ -449,6 +463,38 @@ extern "C" int hc_comm_allreduce_host_staged(hc_comm* c, const float* d_sbuf, fl
     hc_codec_set_timeout_ms(c->host_codec, (unsigned)(c->spin_limit_ns / 1000000ull));
   }
   return hc_allreduce_host_staged(c->host_codec, &c->host_tp, c->rank, c->world, d_sbuf, d_rbuf, count, eb, stream);
+}
+
+extern "C" int hc_comm_set_shares(hc_comm* c, int scatter_ctas_per_sm, int reduce_ctas_per_sm, int reduce_variant) {
+  if (!c || scatter_ctas_per_sm < 0 || reduce_ctas_per_sm < 0 || reduce_variant < 0 || reduce_variant > 2) return hc::kErrArgument;
+  c->share_scatter = scatter_ctas_per_sm;
+  c->share_reduce = reduce_ctas_per_sm;
+  c->reduce_variant = reduce_variant;
+  return hc::kOk;
+}
+
+extern "C" int hc_comm_set_sparse_tiles(hc_comm* c, int on) {
+  if (!c) return hc::kErrArgument;
+  c->sparse = on != 0;
+  return hc::kOk;
+}
+
+// Call numbers tag every arrival flag, so all ranks must count the same calls.  After a call that
+// some rank did not make (or gave up on before enqueueing), the ranks agree on the largest number
+// any of them has reached (over their host channel) and set it everywhere: the next call then uses
+// a number that no stale flag of the broken call carries.
+extern "C" int hc_comm_call_numbers(hc_comm* c, uint32_t out[2]) {
+  if (!c || !out) return hc::kErrArgument;
+  out[0] = c->call;
+  out[1] = c->raw_call;
+  return hc::kOk;
+}
+extern "C" int hc_comm_resync(hc_comm* c, uint32_t call, uint32_t raw_call) {
+  if (!c || call < c->call || raw_call < c->raw_call) return hc::kErrArgument;  // numbers only move forward
+  if (cudaDeviceSynchronize() != cudaSuccess) return hc::kErrCuda;              // nothing of an old call in flight
+  c->call = call;
+  c->raw_call = raw_call;
+  return hc::kOk;
 }
 
 extern "C" int hc_comm_set_overlap(hc_comm* c, int on) {
@@ -539,7 +585,9 @@ struct RawParams {
   uint8_t* peer[hc::kMaxDst];
   uint8_t* mc;                    // multicast alias of the regions (NVLS), or null
   uint64_t s_off, r_off;          // byte offsets of the staging / result areas in a region
-  uint64_t flag_off[3];           // staged, reduced, done rows
+  uint64_t flag_off[4];           // staged, reduced, done, pushed rows
+  float* slice;                   // reduce-scatter: the sum of this rank's chunk goes here only
+  const float* push_src;          // all-gather: this rank's chunk to be stored into every rank's result area
   uint32_t* ctrl;                 // [1] CTA exit counter, [2] status
   uint64_t limit_ns;
 };
@@ -583,9 +631,10 @@ __global__ void __launch_bounds__(256) hc_raw_reduce_kernel(const RawParams p) {
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
   if ((int)threadIdx.x < p.world) {
-    // everybody has staged this call's input and has finished reading the previous call's result
+    // everybody has staged this call's input and (unless the sum stays here) has finished reading
+    // the previous call's result
     bool good = raw_wait(mine + threadIdx.x, p.call, p);
-    if (good && p.call > 1) good = raw_wait(done + threadIdx.x, p.call - 1, p);
+    if (good && p.call > 1 && p.slice == nullptr) good = raw_wait(done + threadIdx.x, p.call - 1, p);
     if (!good) {
       atomicMax(p.ctrl + 2, (uint32_t)hc::kErrPeer);
       ok = 0;
@@ -604,11 +653,16 @@ __global__ void __launch_bounds__(256) hc_raw_reduce_kernel(const RawParams p) {
     uint8_t* R = p.mc + p.r_off + lo * sizeof(float);
     for (uint64_t i = i0; i < n4; i += stride) {
       const float4 acc = hc::dev::multimem_ld_reduce_add_v4(S + 16 * i);
-      hc::dev::multimem_st_v4(R + 16 * i, __float_as_uint(acc.x), __float_as_uint(acc.y), __float_as_uint(acc.z),
-                              __float_as_uint(acc.w));
+      if (p.slice) reinterpret_cast<float4*>(p.slice)[i] = acc;
+      else
+        hc::dev::multimem_st_v4(R + 16 * i, __float_as_uint(acc.x), __float_as_uint(acc.y), __float_as_uint(acc.z),
+                                __float_as_uint(acc.w));
     }
-    for (uint64_t i = n4 * 4 + i0; i < n; i += stride)
-      hc::dev::multimem_st_f32(R + 4 * i, hc::dev::multimem_ld_reduce_add_f32(S + 4 * i));
+    for (uint64_t i = n4 * 4 + i0; i < n; i += stride) {
+      const float acc = hc::dev::multimem_ld_reduce_add_f32(S + 4 * i);
+      if (p.slice) p.slice[i] = acc;
+      else hc::dev::multimem_st_f32(R + 4 * i, acc);
+    }
   } else if (ok && lo < hi) {
     const uint64_t n = hi - lo, n4 = n / 4;  // chunk starts are multiples of 32 floats
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, i0 = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -618,23 +672,67 @@ __global__ void __launch_bounds__(256) hc_raw_reduce_kernel(const RawParams p) {
         const float4 v = __ldcg(reinterpret_cast<const float4*>(p.peer[q] + p.s_off) + lo / 4 + i);
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
       }
-      for (int q = 0; q < p.world; ++q) reinterpret_cast<float4*>(p.peer[q] + p.r_off)[lo / 4 + i] = acc;
+      if (p.slice) reinterpret_cast<float4*>(p.slice)[i] = acc;
+      else
+        for (int q = 0; q < p.world; ++q) reinterpret_cast<float4*>(p.peer[q] + p.r_off)[lo / 4 + i] = acc;
     }
     for (uint64_t i = n4 * 4 + i0; i < n; i += stride) {
       float acc = 0.f;
       for (int q = 0; q < p.world; ++q) acc += __ldcg(reinterpret_cast<const float*>(p.peer[q] + p.s_off) + lo + i);
-      for (int q = 0; q < p.world; ++q) reinterpret_cast<float*>(p.peer[q] + p.r_off)[lo + i] = acc;
+      if (p.slice) p.slice[i] = acc;
+      else
+        for (int q = 0; q < p.world; ++q) reinterpret_cast<float*>(p.peer[q] + p.r_off)[lo + i] = acc;
     }
   }
   raw_publish(p, 1);
 }
 
-__global__ void __launch_bounds__(256) hc_raw_gather_kernel(const RawParams p) {
-  const uint32_t* red = reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.flag_off[1]);
+// all-gather half of the hierarchical allreduce: this rank's chunk (push_src) into the result area of
+// every rank of the group, peer stores or one multimem store per 16 bytes
+__global__ void __launch_bounds__(256) hc_raw_push_kernel(const RawParams p) {
+  const uint32_t* done = reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.flag_off[2]);
   __shared__ uint32_t ok;
   if (threadIdx.x == 0) ok = 1;
   __syncthreads();
-  if ((int)threadIdx.x < p.world && !raw_wait(red + threadIdx.x, p.call, p)) {
+  // everybody has finished reading the previous call's result out of its result area
+  if ((int)threadIdx.x < p.world && p.call > 1 && !raw_wait(done + threadIdx.x, p.call - 1, p)) {
+    atomicMax(p.ctrl + 2, (uint32_t)hc::kErrPeer);
+    ok = 0;
+  }
+  __syncthreads();
+  const uint64_t lo = (uint64_t)p.rank * p.chunk;
+  const uint64_t hi = lo + p.chunk < p.count ? lo + p.chunk : p.count;
+  if (ok && lo < hi) {
+    const uint64_t n = hi - lo, n4 = n / 4;  // chunk starts are multiples of 32 floats
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, i0 = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (uint64_t i = i0; i < n4; i += stride) {
+      const float4 v = reinterpret_cast<const float4*>(p.push_src)[i];
+      if (p.mc)
+        hc::dev::multimem_st_v4(p.mc + p.r_off + (lo + 4 * i) * sizeof(float), __float_as_uint(v.x), __float_as_uint(v.y),
+                                __float_as_uint(v.z), __float_as_uint(v.w));
+      else
+        for (int q = 0; q < p.world; ++q) reinterpret_cast<float4*>(p.peer[q] + p.r_off)[lo / 4 + i] = v;
+    }
+    for (uint64_t i = n4 * 4 + i0; i < n; i += stride) {
+      const float v = p.push_src[i];
+      if (p.mc) hc::dev::multimem_st_f32(p.mc + p.r_off + (lo + i) * sizeof(float), v);
+      else
+        for (int q = 0; q < p.world; ++q) reinterpret_cast<float*>(p.peer[q] + p.r_off)[lo + i] = v;
+    }
+  }
+  raw_publish(p, 3);
+}
+
+__global__ void __launch_bounds__(256) hc_raw_gather_kernel(const RawParams p) {
+  const uint32_t* red = reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.flag_off[1]);
+  const uint32_t* pushed = reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.flag_off[3]);
+  __shared__ uint32_t ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  // every rank is through with reading the staged inputs (row "reduced"); in the hierarchical form the
+  // result area is filled by the push kernels instead (row "pushed")
+  if ((int)threadIdx.x < p.world &&
+      (!raw_wait(red + threadIdx.x, p.call, p) || (p.push_src && !raw_wait(pushed + threadIdx.x, p.call, p)))) {
     atomicMax(p.ctrl + 2, (uint32_t)hc::kErrPeer);
     ok = 0;
   }
@@ -652,14 +750,13 @@ __global__ void __launch_bounds__(256) hc_raw_gather_kernel(const RawParams p) {
 
 }  // namespace
 
-extern "C" int hc_allreduce_raw(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, hc_stream_t stream) {
-  if (!c || !d_sbuf || !d_rbuf) return hc::kErrArgument;
-  if (count == 0) return hc::kOk;
+namespace {
+int raw_params(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, RawParams* out) {
   const Layout& L = c->lay;
   if (count > L.raw_capacity_floats()) return hc::kErrArgument;
   c->raw_call += 1;
   if (c->raw_call == 0) c->raw_call = 1;
-  RawParams p;
+  RawParams& p = *out;
   memset(&p, 0, sizeof(p));
   p.src = d_sbuf;
   p.dst = d_rbuf;
@@ -672,15 +769,67 @@ extern "C" int hc_allreduce_raw(hc_comm* c, const float* d_sbuf, float* d_rbuf, 
   p.mc = c->world > 1 ? c->mc : nullptr;
   p.s_off = 0;
   p.r_off = (uint64_t)L.raw_capacity_floats() * sizeof(float);
-  for (int k = 0; k < 3; ++k) p.flag_off[k] = L.raw_flag(k, 0);
+  for (int k = 0; k < 4; ++k) p.flag_off[k] = L.raw_flag(k, 0);
   p.ctrl = static_cast<uint32_t*>(c->ws_mem) + 32;  // own counters, apart from the codec's
   p.limit_ns = c->spin_limit_ns;
+  return hc::kOk;
+}
+}  // namespace
+
+extern "C" int hc_allreduce_raw(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, hc_stream_t stream) {
+  if (!c || !d_sbuf || !d_rbuf) return hc::kErrArgument;
+  if (count == 0) return hc::kOk;
+  RawParams p;
+  if (int rc = raw_params(c, d_sbuf, d_rbuf, count, &p)) return rc;
   const int grid = hc::device_sm_count() * 4;
   hc_raw_stage_kernel<<<grid, 256, 0, stream>>>(p);
   hc_raw_reduce_kernel<<<grid, 256, 0, stream>>>(p);
   hc_raw_gather_kernel<<<grid, 256, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? hc::kOk : hc::kErrCuda;
 }
+
+// Hierarchical allreduce (mixed_compressed_allreduce, HomComp/src/cuda_awareallreduce.cu:673-706 with
+// its phases at :588-636 and :638-671): raw fp32 reduce-scatter inside the group of `local`, compressed
+// allreduce of this rank's slice of the group sum between the groups (over `inter`, the ranks with the
+// same local index), raw all-gather inside the group.  The reference moves the raw phases with
+// MPI_Isend / MPI_Irecv and a 4-input adder hard-wired to four ranks per node; here they are the
+// peer-memory kernels above for any group size, and the middle phase is hc_allreduce.
+extern "C" int hc_allreduce_mixed(hc_comm* local, hc_comm* inter, const float* d_sbuf, float* d_rbuf, size_t count,
+                                  float eb, hc_stream_t stream) {
+  if (!local || !d_sbuf || !d_rbuf || !(eb > 0.0f)) return hc::kErrArgument;
+  if (count == 0) return hc::kOk;
+  RawParams p;
+  if (int rc = raw_params(local, d_sbuf, d_rbuf, count, &p)) return rc;
+  if (!local->slice) {  // first use (set-up): room for this rank's slice at max_count
+    const size_t floats = hc_chunk_elems(local->max_count, local->world);
+    if (cudaMalloc(&local->slice, (floats ? floats : 1) * sizeof(float)) != cudaSuccess) return hc::kErrCuda;
+  }
+  const uint64_t lo = (uint64_t)p.rank * p.chunk;
+  const uint64_t n_slice = lo >= count ? 0 : (lo + p.chunk < count ? p.chunk : count - lo);
+  if (inter && inter->world > 1 && n_slice > inter->max_count) return hc::kErrArgument;
+  const int grid = hc::device_sm_count() * 4;
+  // 1. reduce-scatter inside the group: the sum of chunk `rank` lands in local->slice
+  p.slice = local->slice;
+  hc_raw_stage_kernel<<<grid, 256, 0, stream>>>(p);
+  hc_raw_reduce_kernel<<<grid, 256, 0, stream>>>(p);
+  if (cudaGetLastError() != cudaSuccess) return hc::kErrCuda;
+  // 2. compressed allreduce of the slice between the groups, in place
+  if (inter && inter->world > 1 && n_slice)
+    if (int rc = hc_allreduce(inter, local->slice, local->slice, (size_t)n_slice, eb, stream)) return rc;
+  // 3. all-gather inside the group
+  p.slice = nullptr;
+  p.push_src = local->slice;
+  hc_raw_push_kernel<<<grid, 256, 0, stream>>>(p);
+  hc_raw_gather_kernel<<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? hc::kOk : hc::kErrCuda;
+}
+
+extern "C" int hc_comm_set_inter(hc_comm* local, hc_comm* inter) {
+  if (!local) return hc::kErrArgument;
+  local->inter = inter;
+  return hc::kOk;
+}
+extern "C" hc_comm* hc_comm_get_inter(hc_comm* local) { return local ? local->inter : nullptr; }
 
 // ---- CUDA IPC helpers ---------------------------------------------------------------------------
 int hc_ipc_alloc(void** d_ptr, size_t bytes, uint8_t handle[64]) {

@@ -149,9 +149,40 @@ int hc_comm_set_algorithm(hc_comm* c, int algorithm);
 // Direct algorithm: launch steps 2 and 3 with programmatic stream serialisation, so that each fills
 // the SMs while its predecessor drains (default on; off while tracing).  Same results either way.
 int hc_comm_set_overlap(hc_comm* c, int on);
+// Direct algorithm with overlap on: how many CTAs per SM step 1 (scatter-compress) and step 2
+// (reduce) may take, so that the three steps of a call run side by side on the GPU, each consuming
+// the tiles of the one before as their flags arrive, instead of one after the other (0: no limit,
+// every step takes the whole GPU as it becomes free).  reduce_variant: 0 launcher's choice, 1 the
+// add kernel with the payload ring, 2 the in-place one.  Results do not depend on any of it.
+int hc_comm_set_shares(hc_comm* c, int scatter_ctas_per_sm, int reduce_ctas_per_sm, int reduce_variant);
+// Transport buffers between the steps of a call: tiles at fixed offsets, as if every block before
+// them were incompressible (default), or packed back to back as in a stored stream (0).  With fixed
+// offsets no CTA waits for a prefix over other CTAs' tiles; the buffers are sized for the worst case
+// either way, only the bytes of the payload are ever written or read, and consumers take each tile's
+// offset from its arrival flag.  Results and hc_comm_last_stream_bytes do not depend on it.
+int hc_comm_set_sparse_tiles(hc_comm* c, int on);
 // Uncompressed sum over the same peer mappings (two-shot direct algorithm, three kernels); the
 // compressed and the uncompressed collective of one handle must not be in flight together.
 int hc_allreduce_raw(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, hc_stream_t stream);
+// Hierarchical allreduce for ranks that form groups (nodes, or halves of one NVSwitch box): raw fp32
+// reduce-scatter inside the group of `local`, hc_allreduce (error bound eb) of this rank's slice of
+// the group sum over `inter` (the ranks with the same local index in the other groups; NULL or a
+// world of 1: one group, nothing is compressed), raw all-gather inside the group.  The result is
+// identical on every rank of every group.  inter must take hc_chunk_elems(count, local world) values.
+// Seven kernels on `stream` (4 raw + the 3 of hc_allreduce); the first call allocates the slice buffer.
+int hc_allreduce_mixed(hc_comm* local, hc_comm* inter, const float* d_sbuf, float* d_rbuf, size_t count, float eb,
+                       hc_stream_t stream);
+// Attaches `inter` to `local` for the reference-named mixed_compressed_allreduce (homcomp_compat.h),
+// whose signature has room for one communicator only.
+int hc_comm_set_inter(hc_comm* local, hc_comm* inter);
+hc_comm* hc_comm_get_inter(hc_comm* local);
+// Recovery after a call that not every rank made (a rank raised an error on the host, skipped a
+// step, was restarted): the others' kernels run into their time-out and report status 6, nothing
+// hangs.  To go on, every rank reads its call numbers, the ranks agree on the element-wise maximum
+// over their host channel, every rank sets it with hc_comm_resync (synchronises the device) and
+// clears its status; the next hc_allreduce is then an ordinary one.
+int hc_comm_call_numbers(hc_comm* c, uint32_t out[2]);  // [0] compressed calls, [1] uncompressed / hierarchical calls
+int hc_comm_resync(hc_comm* c, uint32_t call, uint32_t raw_call);
 // Tracing: with trace on, hc_allreduce records one CUDA event per step; hc_comm_last_step_ms returns
 // the device time of each step of the last call (reduce-scatter steps, then the decode).
 int hc_comm_set_trace(hc_comm* c, int on);

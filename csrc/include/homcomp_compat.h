@@ -8,7 +8,16 @@
 //   * scratch memory is kept per device between calls instead of cudaMalloc / cudaFree per call;
 //   * `MPI_Comm` is this library's communicator handle unless <mpi.h> was included first: no MPI
 //     is needed, ranks are bootstrapped with hc_comm_create (any host channel for the handles);
-//   * errors come back as a non-zero status instead of exit() / MPI_Abort().
+//   * errors come back as a non-zero status instead of exit() / MPI_Abort(); the void functions print
+//     a line to stderr and leave the code in hc_compat_last_status.
+//
+// Output buffers.  The signatures carry no capacity, so it is assumed.  By default a compressed
+// output buffer (d_cmpBytes, d_cmpByteOut, cmpBytes) is taken to hold nbEle * 4 bytes, which is
+// what every caller in the reference allocates; a stream that would not fit (incompressible
+// data needs up to 129 bytes per 128) is cut off at that size, status 1 is reported, *cmpSize is 0,
+// and nothing is written past nbEle * 4 bytes.  A caller that allocates
+// hc_max_compressed_bytes(nbEle) bytes, which always suffices, says so once with
+// hc_compat_set_capacity_rule(1).
 #pragma once
 #include <cuda_runtime.h>
 #include <stddef.h>
@@ -19,6 +28,10 @@
 typedef hc_comm* MPI_Comm;
 #define HC_COMPAT_OWN_MPI_COMM 1
 #endif
+
+// 0 (default): output buffers hold nbEle * 4 bytes; 1: they hold hc_max_compressed_bytes(nbEle)
+void hc_compat_set_capacity_rule(int rule);
+extern int hc_compat_last_status;  // last non-zero status of a void entry point (0: none so far)
 
 void GSZ_compress_hostptr(float* oriData, unsigned char* cmpBytes, size_t nbEle, size_t* cmpSize, float errorBound);
 void GSZ_decompress_hostptr(float* decData, unsigned char* cmpBytes, size_t nbEle, size_t cmpSize, float errorBound);

@@ -20,13 +20,17 @@
 //   * The FIRST call on each device looks up the array's device address (cudaGetSymbolAddress,
 //     with that device current) and registers the kernel's shared-memory size.  Make that first
 //     call before any stream capture begins.
-//   * Every call on a device uses the same array.  The state that must start from zero is cleared
-//     on the caller's stream at the start of each call; everything else is tagged with a call
-//     number, so contents left by the previous call are ignored.  Two calls that can overlap on
-//     the GPU (different streams without an ordering between them, or two host threads) race on
-//     that state: order them.
+//   * Every call on a device uses the same array, which keeps what the last call left in it.  The
+//     counters that must start from zero are put back by the kernel itself when its last block
+//     leaves, and everything else is tagged with a call number, so stale contents are ignored.
+//     Two calls that can overlap on the GPU (different streams without an ordering between them,
+//     or two host threads) race on that state: order them.
+//   * Errors found on the device (output buffer too small: 1, a wait that ran out: 3) land in a
+//     sticky word of the array; the call itself has returned 0 long before.  hc_noalloc_status
+//     reads it.  When the buffer was too small *d_size is not written.  A time-out stays in force
+//     (later calls produce nothing) until hc_noalloc_status(1) has cleared it.
 //   * The call makes no cudaMalloc / cudaFree and uses no allocating library routine; it enqueues
-//     one small memset and one kernel on `stream` and returns without synchronising.
+//     one kernel on `stream` and returns without synchronising.
 //
 // Output is byte-identical to hc_compress with mode 0 (outlier codec).
 #pragma once
@@ -45,6 +49,11 @@ extern "C" {
 // d_size: device word that receives the exact stream length.  Returns 0 or a hc::Status code.
 int hc_compress_noalloc(const float* d_x, size_t n, float eb, uint8_t* d_out, size_t cap, uint64_t* d_size,
                         hc_stream_t stream);
+// Synchronises the current device and returns the sticky device status of hc_compress_noalloc on it
+// (0 ok, 1 output capacity exceeded, 3 a bounded wait ran out); clear != 0 also resets it.
+int hc_noalloc_status(int clear);
+// Upper bound of the kernel's waits (default 2000 ms); applies to later calls of this process.
+int hc_noalloc_set_timeout_ms(unsigned ms);
 // Bytes of the built-in scratch array (for the curious; the caller never touches it).
 size_t hc_noalloc_scratch_bytes(void);
 

@@ -1,5 +1,6 @@
-// Minimal single-host MPI for building the reference library where no MPI is installed.
-// Only what HomComp/src/cuda_awareallreduce.cu uses.  Ranks are processes on one machine (started
+// Minimal single-host MPI for machines where no MPI is installed: enough for this library's MPI
+// front door (homcomp_mpi.h) and for building the reference library (what
+// HomComp/src/cuda_awareallreduce.cu uses).  Ranks are processes on one machine (started
 // by torch.distributed.run or any launcher that sets RANK / WORLD_SIZE / MASTER_PORT); messages
 // between device buffers travel GPU to GPU through persistent, IPC-mapped device mailboxes (what a
 // CUDA-aware MPI does inside one node), matched in FIFO order per (source, destination) pair.

@@ -72,7 +72,7 @@ def _raw_worker(rank, world):
         assert ar.status() == 0
         torch.testing.assert_close(out.cpu(), want, rtol=0, atol=0)
     out2 = torch.zeros_like(x)
-    collectives.mixed_compressed_allreduce(ar, x, out2, 1e-4)
+    collectives.mixed_compressed_allreduce(ar, x, out2, 1e-4)  # one group: nothing is compressed
     torch.testing.assert_close(out2.cpu(), want, rtol=0, atol=0)
     # host-staged variant: same numbers as the device ring
     out3 = torch.zeros_like(x)
@@ -147,3 +147,42 @@ def test_allreduce_over_multicast_transport(tmp_path):
     run_ranks(_nvls_worker, world, args=([1, 4097, 100000, (1 << 22) + 12345], 1e-4, str(note)), backend="nccl")
     if note.read_text() != "1":
         pytest.skip("the fabric offers no multicast mapping: ran over peer stores on symmetric memory")
+
+
+def _hier_worker(rank, world, group_size, counts, eb):
+    """mixed_compressed_allreduce with the ranks split into groups: raw inside a group, compressed
+    between the groups; compared with the host oracle composed the same way, bit for bit on every rank."""
+    import torch.distributed as dist
+
+    from datasets import gradient_like, smooth
+    from tirocinio_triennale_b200.parallel import collectives
+
+    local, inter = collectives.make_hierarchy(max(counts), group_size, timeout_ms=5000)
+    for it, n in enumerate(counts):
+        gen = smooth if it % 2 == 0 else gradient_like
+        bufs = [gen(n, seed=300 * it + r) for r in range(world)]
+        want = collectives.hierarchy_oracle(bufs, group_size, eb)
+        x = torch.from_numpy(bufs[rank]).cuda()
+        for rep in range(2):  # twice: flags, slots and the result area are reused without any reset
+            out = torch.full_like(x, -3.0)
+            collectives.mixed_compressed_allreduce(local, x, out, eb, inter_comm=inter)
+            assert local.status() == 0 and (inter is None or inter.status() == 0)
+            np.testing.assert_array_equal(out.cpu().numpy(), want)
+        exact = np.sum(np.stack(bufs).astype(np.float64), axis=0)
+        n_groups = world // group_size
+        assert np.abs(want - exact).max() <= n_groups * eb * 1.01 + 1e-5
+        # the flat uncompressed call of the same handle still works in between (shared call counter)
+        out2 = torch.zeros_like(x)
+        local.allreduce_raw(x, out2)
+        assert local.status() == 0
+    dist.barrier()
+    if inter is not None:
+        inter.close()
+    local.close()
+
+
+@pytest.mark.parametrize("world,group_size", [(2, 1), (2, 2), (4, 2), (8, 4), (8, 2)])
+def test_hierarchical_allreduce_matches_composed_oracle(world, group_size):
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    run_ranks(_hier_worker, world, args=(group_size, [33, 100_003, (1 << 21) + 77], 1e-4))

@@ -56,3 +56,58 @@ def test_corrupted_rate_bytes_are_contained():
     assert y.numel() == n
     out, size = codec.compress(torch.from_numpy(x).cuda(), eb)  # still usable
     assert codec.status() == 0
+
+
+def _missing_peer(rank, world):
+    """A rank that is alive but sits one call out.  Host-made failure: no kernel faults or hangs; the
+    other rank's bounded waits run out, it reads status 6, the ranks realign their call numbers over
+    the host channel and the next call is an ordinary one.  Peer stores over CUDA IPC only (no
+    multicast), short time-out, nobody leaves before close()."""
+    import numpy as np
+    import torch.distributed as dist
+
+    from datasets import gradient_like
+    from tirocinio_triennale_b200 import ops
+    from tirocinio_triennale_b200.parallel import CompressedAllreduce
+
+    n, eb = 600_000, 1e-4
+    ar = CompressedAllreduce(n, timeout_ms=300, transport="ipc")
+    bufs = [gradient_like(n, seed=40 + r) for r in range(world)]
+    want = ops.cpu_ring_allreduce(bufs, eb)[rank]
+    x = torch.from_numpy(bufs[rank]).cuda()
+    out = torch.empty_like(x)
+    for algorithm in ("direct", "ring"):
+        ar.set_algorithm(algorithm)
+        ar.allreduce(x, out, eb)
+        assert ar.status() == 0
+        np.testing.assert_array_equal(out.cpu().numpy(), want)
+        dist.barrier()
+        # the broken call: rank 1 skips it on the host
+        if rank != 1:
+            t0 = torch.cuda.Event(enable_timing=True)
+            t1 = torch.cuda.Event(enable_timing=True)
+            t0.record()
+            ar.allreduce(x, out, eb)
+            t1.record()
+            torch.cuda.synchronize()
+            assert ar.status(clear=False) == 6  # a peer never arrived
+            assert t0.elapsed_time(t1) < 5000.0  # the waits gave up, one time-out deep per step at most
+        dist.barrier()
+        cleared = ar.resync()
+        assert cleared == (6 if rank != 1 else 0)
+        for _ in range(2):  # both all-gather buffer sets
+            out.fill_(-1.0)
+            ar.allreduce(x, out, eb)
+            assert ar.status() == 0
+            np.testing.assert_array_equal(out.cpu().numpy(), want)
+    dist.barrier()
+    ar.close()
+
+
+@pytest.mark.multigpu
+def test_peer_that_skips_a_call_then_resync():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from mp_util import run_ranks
+
+    run_ranks(_missing_peer, 2)

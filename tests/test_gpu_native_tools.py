@@ -23,6 +23,15 @@ def test_homcomp_eval_tool():
     assert "status no error" in r.stdout
 
 
+def test_reference_named_entry_points_and_their_capacity_rule():
+    """compat_check: round trips through the GSZ_* / homomorphic_sum_F names, and incompressible input
+    (31 bit planes in every block) with a canary behind the output buffer under both capacity rules."""
+    exe = _tools()["compat_check"]
+    r = subprocess.run([str(exe), "1000003"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert r.stdout.strip().endswith("ok") and "FAIL" not in r.stdout
+
+
 @pytest.mark.multigpu
 def test_allreduce_threads_tool():
     n = min(torch.cuda.device_count(), 8)

@@ -41,19 +41,31 @@ def test_noalloc_entry_matches_regular_entry_twice():
     lib.hc_noalloc_scratch_bytes.restype = C.c_size_t
     assert 0 < lib.hc_noalloc_scratch_bytes() <= 1 << 20  # a modest, fixed footprint
 
+    lib.hc_noalloc_status.restype = C.c_int
+    lib.hc_noalloc_status.argtypes = [C.c_int]
+
     eb = 1e-4
     g = torch.Generator(device="cuda").manual_seed(7)
+    # one warm-up call: the first call on a device loads the kernel and looks the array up
+    w = torch.randn(4096, device="cuda", generator=g)
+    wout = torch.zeros(int(lib.hc_max_compressed_bytes(4096)) + 64, dtype=torch.uint8, device="cuda")
+    wsize = torch.zeros(1, dtype=torch.int64, device="cuda")
+    assert fn(w.data_ptr(), 4096, eb, wout.data_ptr(), wout.numel(), wsize.data_ptr(),
+              torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
     sizes = [1_000_003, 250_001]  # the second call is shorter: stale look-back words stay behind it
     for call, n in enumerate(sizes):
         x = torch.randn(n, device="cuda", generator=g) * (0.01 * (call + 1))
         cap = int(lib.hc_max_compressed_bytes(n)) + 64
         out = torch.zeros(cap, dtype=torch.uint8, device="cuda")
         size = torch.zeros(1, dtype=torch.int64, device="cuda")
-        before = torch.cuda.memory_allocated()
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]  # cudaMemGetInfo: sees any cudaMalloc, not only torch's
         rc = fn(x.data_ptr(), n, eb, out.data_ptr(), cap, size.data_ptr(), torch.cuda.current_stream().cuda_stream)
         assert rc == 0
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == free_before
+        assert lib.hc_noalloc_status(0) == 0
         got = out[: int(size.item())].cpu().numpy()
         want = _compress_regular(lib, x, eb, cap)
         assert got.size == want.size
@@ -62,3 +74,16 @@ def test_noalloc_entry_matches_regular_entry_twice():
     # sizes beyond the built-in scratch are refused, loudly and without touching anything
     too_big = 16 * 1024 * 1024 + 1
     assert fn(x.data_ptr(), too_big, eb, out.data_ptr(), cap, size.data_ptr(), 0) == 4
+
+    # an output buffer that is too small: the call is accepted, the device notes status 1, the size word
+    # stays as it was, and the status survives until it is read and cleared
+    size.fill_(-1)
+    small = int(lib.hc_rate_bytes(n)) + 128
+    assert fn(x.data_ptr(), n, eb, out.data_ptr(), small, size.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+    assert lib.hc_noalloc_status(0) == 1
+    assert int(size.item()) == -1
+    assert lib.hc_noalloc_status(1) == 1
+    assert lib.hc_noalloc_status(0) == 0
+    assert fn(x.data_ptr(), n, eb, out.data_ptr(), cap, size.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(out[: int(size.item())].cpu().numpy(), want)

@@ -106,7 +106,31 @@ def build_cuda(force: bool = False, verbose: bool = False, timeline: bool = Fals
     return lib
 
 
-CLI_SOURCES = ["cli/homcomp_eval.cu", "cli/allreduce_threads.cu"]
+def build_mpi(mpi_include: str | None = None, mpi_sources=(), mpi_link=(), force: bool = False) -> Path:
+    """``libhomcomp_b200_mpi.so``: the MPI front door (csrc/cuda/hc_mpi.cu, ``-DHC_WITH_MPI``) next to the
+    main library.  ``mpi_include`` is the directory of ``mpi.h``, ``mpi_link`` extra linker arguments
+    (e.g. ``["-lmpi"]``), ``mpi_sources`` extra sources to compile in.  With no arguments the single-host
+    MPI of csrc/mpi_shim is compiled in, which is all a machine without MPI needs."""
+    base = build_cuda()
+    lib = LIBDIR / "libhomcomp_b200_mpi.so"
+    if mpi_include is None:
+        mpi_include = str(CSRC / "mpi_shim")
+        mpi_sources = [str(CSRC / "mpi_shim" / "mpi_shim.cpp")]
+        mpi_link = ["-lrt"]
+    if not (force or _stale(lib) or lib.stat().st_mtime < base.stat().st_mtime):
+        return lib
+    nvcc = nvcc_path()
+    if nvcc is None:
+        raise RuntimeError("nvcc not found")
+    tmp = lib.with_suffix(".so.tmp%d" % os.getpid())
+    _run([nvcc, *NVCC_FLAGS, "-DHC_WITH_MPI", "-shared", "-I", mpi_include, "-I", str(CSRC / "include"),
+          "-I", str(CSRC / "cuda"), str(CSRC / "cuda" / "hc_mpi.cu"), *mpi_sources, "-o", str(tmp), "-L", str(LIBDIR),
+          "-lhomcomp_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN", "-lcudart", *mpi_link])
+    os.replace(tmp, lib)
+    return lib
+
+
+CLI_SOURCES = ["cli/homcomp_eval.cu", "cli/allreduce_threads.cu", "cli/compat_check.cu"]
 BINDIR = Path(__file__).resolve().parent / "bin"
 
 
@@ -132,3 +156,4 @@ if __name__ == "__main__":
     if "--timeline" in sys.argv:
         print(build_cuda(force="--force" in sys.argv, timeline=True))
     print(build_cli(force="--force" in sys.argv))
+    print(build_mpi(force="--force" in sys.argv))

@@ -25,10 +25,16 @@ def declare(lib):
         "hc_comm_status": [vp, i],
         "hc_allreduce": [vp, vp, vp, sz, f, vp],
         "hc_allreduce_raw": [vp, vp, vp, sz, vp],
+        "hc_allreduce_mixed": [vp, vp, vp, vp, sz, f, vp],
+        "hc_comm_set_inter": [vp, vp],
+        "hc_comm_call_numbers": [vp, C.POINTER(C.c_uint32)],
+        "hc_comm_resync": [vp, C.c_uint32, C.c_uint32],
         "hc_allreduce_host": [vp, vp, vp, sz, f, i, vp],
         "hc_comm_set_trace": [vp, i],
         "hc_comm_set_algorithm": [vp, i],
         "hc_comm_set_overlap": [vp, i],
+        "hc_comm_set_shares": [vp, i, i, i],
+        "hc_comm_set_sparse_tiles": [vp, i],
         "hc_comm_last_step_ms": [vp, C.POINTER(C.c_float), i],
         "hc_comm_last_stream_bytes": [vp, C.POINTER(C.c_uint64), i],
         "hc_allreduce_host_staged": [vp, C.POINTER(HostTransport), i, i, vp, vp, sz, f, vp],

@@ -75,7 +75,11 @@ def _decompress(stream: np.ndarray, n: int, eb: float, mode: str, device) -> tor
         padded = np.zeros(stream.size + 64, dtype=np.uint8)
         padded[: stream.size] = stream
         s = torch.from_numpy(padded).to(device)
-        return codec.decompress(s, n, eb, mode=mode, stream_bytes=stream.size)
+        out = codec.decompress(s, n, eb, mode=mode, stream_bytes=stream.size)
+        st = codec.status()
+        if st != 0:  # e.g. 2: the body is shorter than its rate bytes imply (cut-off or corrupted file)
+            raise ValueError("corrupt stream: the device decoder reported status %d" % st)
+        return out
     return torch.from_numpy(cpu_codec.cpu_decompress(stream, n, eb, mode=mode))
 
 
@@ -136,7 +140,8 @@ def save_state(path, state: dict, eb: float, min_elems: int = 4096, mode: str = 
 def load_state(path, device="cpu") -> dict:
     out = {}
     with zipfile.ZipFile(path, "r") as z:
-        plain = torch.load(io.BytesIO(z.read("rest.pt")), map_location="cpu", weights_only=False)
+        # tensors, python scalars and the ("__hcz__", member) marker tuples only: nothing that needs pickle code
+        plain = torch.load(io.BytesIO(z.read("rest.pt")), map_location="cpu", weights_only=True)
         for k, v in plain.items():
             if isinstance(v, tuple) and len(v) == 2 and v[0] == "__hcz__":
                 out[k] = loads_tensor(z.read(v[1]), device)

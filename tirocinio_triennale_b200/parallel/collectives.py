@@ -182,25 +182,73 @@ def node_layout(group=None):
 
 def mixed_compressed_allreduce(comm: CompressedAllreduce, d_sbuf, d_rbuf, eb: float, inter_comm=None):
     """Hierarchical allreduce (HomComp/src/cuda_awareallreduce.cu:673-706): raw fp32 reduce-scatter
-    inside the node, compressed allreduce of every local rank's slice between nodes, raw
-    all-gather inside the node.
+    inside the group, compressed allreduce of every local rank's slice between the groups, raw
+    all-gather inside the group (``hc_allreduce_mixed``).
 
-    ``comm`` spans the ranks of this node, ``inter_comm`` (optional) the ranks with the same local
-    index on the other nodes.  On a single NVSwitch node there is no inter-node phase and the call
-    is the uncompressed two-shot allreduce, exactly as the reference's version degenerates when
-    every rank shares a node.
+    ``comm`` spans the ranks of this group (the reference takes the ranks that share a node),
+    ``inter_comm`` the ranks with the same local index in the other groups; it must take
+    ``ops.chunk_elems(n, comm.world)`` values.  Without it there is one group and nothing is compressed,
+    exactly as the reference's version degenerates when every rank shares a node.  ``make_hierarchy``
+    builds both handles from a group size.
     """
-    if inter_comm is None or inter_comm.world == 1:
-        return comm.allreduce_raw(d_sbuf, d_rbuf)
-    # node-local sum first, then the compressed exchange of this rank's slice between the nodes,
-    # then redistribution inside the node (the raw kernels already leave the full node-local sum
-    # on every local rank, so the slice exchange is followed by one more raw step)
-    comm.allreduce_raw(d_sbuf, d_rbuf)
-    n = d_rbuf.numel()
-    per = (n + comm.world - 1) // comm.world
-    lo, hi = min(n, comm.rank * per), min(n, (comm.rank + 1) * per)
-    keep = d_rbuf[lo:hi].clone()
-    inter_comm.allreduce(keep, keep, eb)
-    d_rbuf.zero_()
-    d_rbuf[lo:hi].copy_(keep)
-    return comm.allreduce_raw(d_rbuf, d_rbuf)
+    import ctypes as C
+
+    from .. import _lib
+
+    if d_sbuf.dtype != torch.float32 or not d_sbuf.is_cuda or not d_sbuf.is_contiguous() \
+            or d_rbuf.dtype != torch.float32 or not d_rbuf.is_cuda or not d_rbuf.is_contiguous() \
+            or d_rbuf.numel() != d_sbuf.numel():
+        raise ValueError("expected contiguous float32 CUDA tensors of the same size")
+    with torch.cuda.device(comm.device):
+        _lib.check(comm.lib.hc_allreduce_mixed(comm._h, inter_comm._h if inter_comm is not None else None,
+                                               d_sbuf.data_ptr(), d_rbuf.data_ptr(), d_sbuf.numel(), eb,
+                                               torch.cuda.current_stream().cuda_stream), "allreduce_mixed")
+    return d_rbuf
+
+
+def make_hierarchy(max_count: int, group_size: int, transport: str | None = None, timeout_ms: int | None = None):
+    """(local, inter) handles for ``mixed_compressed_allreduce``: consecutive ranks form groups of
+    ``group_size`` (one node each in a multi-node job; halves or quarters of one NVSwitch box otherwise),
+    ``inter`` joins the ranks with the same index in every group.  Collective over the default group."""
+    from ..ops import chunk_elems
+
+    world, rank = dist.get_world_size(), dist.get_rank()
+    if group_size < 1 or world % group_size:
+        raise ValueError("the world size must be a multiple of the group size")
+    n_groups = world // group_size
+    local_groups = [dist.new_group(list(range(g * group_size, (g + 1) * group_size))) for g in range(n_groups)]
+    inter_groups = [dist.new_group(list(range(l, world, group_size))) for l in range(group_size)]
+    local = CompressedAllreduce(max_count, group=local_groups[rank // group_size], transport=transport,
+                                timeout_ms=timeout_ms)
+    inter = None
+    if n_groups > 1:
+        inter = CompressedAllreduce(max(1, chunk_elems(max_count, group_size)), group=inter_groups[rank % group_size],
+                                    transport=transport, timeout_ms=timeout_ms)
+    return local, inter
+
+
+def hierarchy_oracle(bufs, group_size: int, eb: float):
+    """Host restatement of ``mixed_compressed_allreduce`` for ``len(bufs)`` ranks (numpy float32 arrays):
+    group sums in fp32 in rank order, the host-rank compressed ring between the groups slice by slice.
+    Bit-exact expectation for the ``ipc`` transport (a multicast mapping adds in the switch's order)."""
+    import numpy as np
+
+    from ..ops import chunk_elems, cpu_ring_allreduce
+
+    world, n = len(bufs), bufs[0].size
+    n_groups = world // group_size
+    sums = []
+    for g in range(n_groups):
+        acc = np.zeros(n, dtype=np.float32)
+        for l in range(group_size):
+            acc = (acc + bufs[g * group_size + l].astype(np.float32)).astype(np.float32)
+        sums.append(acc)
+    if n_groups == 1:
+        return sums[0]
+    out = np.zeros(n, dtype=np.float32)
+    B = chunk_elems(n, group_size)
+    for l in range(group_size):
+        lo, hi = min(n, l * B), min(n, (l + 1) * B)
+        if hi > lo:
+            out[lo:hi] = cpu_ring_allreduce([s[lo:hi] for s in sums], eb)[0]
+    return out

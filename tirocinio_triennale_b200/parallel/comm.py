@@ -142,6 +142,21 @@ class CompressedAllreduce:
         with torch.cuda.device(self.device):
             return int(self.lib.hc_comm_status(self._h, 1 if clear else 0))
 
+    def resync(self) -> int:
+        """Collective over the host group.  After a call that some rank did not make (its peers got
+        status 6 when their bounded waits ran out), brings the ranks' call numbers back in line, so
+        that the handle can be used again; clears the sticky status.  Returns the status it cleared."""
+        nums = (C.c_uint32 * 2)()
+        _lib.check(self.lib.hc_comm_call_numbers(self._h, nums), "call_numbers")
+        everybody = [None] * self.world
+        dist.all_gather_object(everybody, (int(nums[0]), int(nums[1])), group=self.group)
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.hc_comm_resync(self._h, max(e[0] for e in everybody), max(e[1] for e in everybody)),
+                       "resync")
+            st = self.status(clear=True)
+        dist.barrier(group=self.group)
+        return st
+
     def set_algorithm(self, algorithm: str):
         """``"ring"``: one fused kernel per reduce-scatter hop (world + 1 launches, the reference's
         algorithm); ``"direct"``: scatter, reduce, gather in three launches (default).  Same bits."""
@@ -153,6 +168,18 @@ class CompressedAllreduce:
         """Direct algorithm: let steps 2 and 3 start while their predecessor drains (programmatic
         dependent launch; default on, ignored while tracing).  Results do not depend on it."""
         _lib.check(self.lib.hc_comm_set_overlap(self._h, 1 if on else 0), "set_overlap")
+
+    def set_shares(self, scatter_ctas_per_sm: int = 0, reduce_ctas_per_sm: int = 0, reduce_variant: int = 0):
+        """Direct algorithm: CTAs per SM that the scatter and reduce steps may take (0: no limit), so that
+        the three steps of a call share the GPU and run side by side; ``reduce_variant`` 0 auto, 1 ring,
+        2 in place.  Results do not depend on it."""
+        _lib.check(self.lib.hc_comm_set_shares(self._h, int(scatter_ctas_per_sm), int(reduce_ctas_per_sm),
+                                               int(reduce_variant)), "set_shares")
+
+    def set_sparse_tiles(self, on: bool = True):
+        """Tiles at fixed offsets in the transport buffers (default; no CTA waits for a prefix over other
+        CTAs' tiles) or packed back to back (``False``).  Results do not depend on it."""
+        _lib.check(self.lib.hc_comm_set_sparse_tiles(self._h, 1 if on else 0), "set_sparse_tiles")
 
     def set_trace(self, on: bool = True):
         """Record one CUDA event per step of every following allreduce (see ``last_step_ms``)."""
