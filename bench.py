@@ -198,7 +198,7 @@ def run_ours(args, rank, world, local):
         "implementation": {
             "algorithm_timed": "direct (scatter-compress, fused reduce, decode: 3 kernels per call over peer memory)"
                                if world > 1 else "compress + decode (2 kernels per call)",
-            "e2e_call": "CompressedAllreduce.allreduce_host: the message crosses PCIe in 8 pieces on two copy streams "
+            "e2e_call": "CompressedAllreduce.allreduce_host: the message crosses PCIe in 16 pieces on two copy streams "
                         "while earlier pieces are reduced and sent back",
         },
         "per_rank_gbs": per_rank,

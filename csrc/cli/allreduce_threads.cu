@@ -8,7 +8,12 @@
 // (mixed_compressed_allreduce) with the GPUs split into two groups: raw inside a group, compressed
 // between the two.
 //
-//   allreduce_threads [gpus] [count] [eb] [iterations]
+// With `nvls` as the fifth argument the symmetric regions come from hc_mc_create_local (driver virtual
+// memory API + multicast object) instead of cudaMalloc + peer access: the reduced chunks then leave
+// with one multimem.st for all GPUs and the uncompressed sum is formed inside the switch.  The line
+// ends with a checksum of rank 0's compressed-allreduce result, which must not depend on the transport.
+//
+//   allreduce_threads [gpus] [count] [eb] [iterations] [ipc|nvls]
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdio.h>
@@ -83,6 +88,7 @@ int main(int argc, char** argv) {
   const size_t count = argc > 2 ? (size_t)atoll(argv[2]) : (size_t)1 << 22;
   const float eb = argc > 3 ? (float)atof(argv[3]) : 1e-4f;
   const int iters = argc > 4 ? atoi(argv[4]) : 10;
+  const bool nvls = argc > 5 && strcmp(argv[5], "nvls") == 0;
   if (P < 1 || P > ndev || P > 8) {
     fprintf(stderr, "need 1..%d GPUs\n", ndev < 8 ? ndev : 8);
     return 2;
@@ -101,13 +107,28 @@ int main(int argc, char** argv) {
   std::vector<void*> region_local(P, nullptr), region_inter(P, nullptr);
   std::vector<Mailbox> boxes((size_t)P * P);
   Barrier bar(P);
+  unsigned long long checksum = 0;
+  hc_mc_region* mc_region = nullptr;
+  void* mc_base = nullptr;
+  if (nvls) {
+    std::vector<int> devs(P);
+    for (int r = 0; r < P; ++r) devs[r] = r;
+    if (hc_mc_create_local(&mc_region, P, devs.data(), sym) != 0) {
+      fprintf(stderr, "hc_mc_create_local failed\n");
+      return 2;
+    }
+    for (int r = 0; r < P; ++r) region[r] = hc_mc_unicast_ptr(mc_region, r);
+    mc_base = hc_mc_multicast_ptr(mc_region);
+  }
   auto worker = [&](int r) {
     int sense = 0;
     cudaSetDevice(r);
     for (int q = 0; q < P; ++q)
       if (q != r) cudaDeviceEnablePeerAccess(q, 0);
-    cudaMalloc(&region[r], sym);
-    cudaMemset(region[r], 0, sym);
+    if (!nvls) {
+      cudaMalloc(&region[r], sym);
+      cudaMemset(region[r], 0, sym);
+    }
     if (mixed) {
       cudaMalloc(&region_local[r], sym_local);
       cudaMemset(region_local[r], 0, sym_local);
@@ -117,7 +138,7 @@ int main(int argc, char** argv) {
     cudaDeviceSynchronize();
     bar.wait(sense);
     hc_comm* comm = nullptr;
-    if (hc_comm_create(&comm, r, P, count, region.data(), nullptr) != 0) { failures[r] = 1; return; }
+    if (hc_comm_create(&comm, r, P, count, region.data(), mc_base) != 0) { failures[r] = 1; return; }
     hc_comm *local = nullptr, *inter = nullptr;
     if (mixed) {
       const int g = r / L, l = r % L;
@@ -165,6 +186,12 @@ int main(int argc, char** argv) {
       if (bad || hc_comm_status(comm, 1) != 0) failures[r] = 1;
       if (mode == 3 && (hc_comm_status(local, 1) != 0 || hc_comm_status(inter, 1) != 0)) failures[r] = 1;
       if (bad) fprintf(stderr, "rank %d mode %d: %zu values out of tolerance\n", r, mode, bad);
+      if (r == 0 && mode == 0) {  // FNV-1a over the result bytes
+        unsigned long long h = 1469598103934665603ull;
+        const unsigned char* b = reinterpret_cast<const unsigned char*>(out.data());
+        for (size_t i = 0; i < count * 4; ++i) h = (h ^ b[i]) * 1099511628211ull;
+        checksum = h;
+      }
     }
     bar.wait(sense);
     hc_comm_destroy(comm);
@@ -173,7 +200,7 @@ int main(int argc, char** argv) {
     cudaFree(d_in);
     cudaFree(d_out);
     bar.wait(sense);
-    cudaFree(region[r]);
+    if (!nvls) cudaFree(region[r]);
     if (mixed) {
       cudaFree(region_local[r]);
       cudaFree(region_inter[r]);
@@ -182,6 +209,7 @@ int main(int argc, char** argv) {
   std::vector<std::thread> th;
   for (int r = 0; r < P; ++r) th.emplace_back(worker, r);
   for (auto& t : th) t.join();
+  if (mc_region) hc_mc_destroy(mc_region);
   float mc = 0, mr = 0, mh = 0, mm = 0;
   int fail = 0;
   for (int r = 0; r < P; ++r) {
@@ -192,7 +220,9 @@ int main(int argc, char** argv) {
     fail |= failures[r];
   }
   printf("gpus %d count %zu eb %g | compressed allreduce %.3f ms (%.1f GB/s) | uncompressed %.3f ms (%.1f GB/s) | "
-         "host-staged %.3f ms | hierarchical (2 groups of %d) %.3f ms | %s\n",
-         P, count, eb, mc, 4e-6 * count / mc, mr, 4e-6 * count / mr, mh, mixed ? L : 0, mm, fail ? "FAILED" : "ok");
+         "host-staged %.3f ms | hierarchical (2 groups of %d) %.3f ms | transport %s | checksum %016llx | %s\n",
+         P, count, eb, mc, 4e-6 * count / mc, mr, 4e-6 * count / mr, mh, mixed ? L : 0, mm,
+         nvls ? (mc_base ? "nvls (multicast)" : "nvls asked, no multicast support: peer stores") : "ipc", checksum,
+         fail ? "FAILED" : "ok");
   return fail;
 }

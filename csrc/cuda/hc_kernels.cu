@@ -488,7 +488,8 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
         sh.out_base[r] = goff;
         sh.out_ok[r] = ok ? 1u : 0u;
         mbar_arrive(&sh.base_ready[r]);
-        if (!p.sparse && ok && v.lt == p.tiles_per_seg - 1 && p.size_out) p.size_out[v.g] = goff + tot;
+        // the last tile ends where the stream ends: no size for a stream that did not fit
+        if (!p.sparse && ok && v.lt == p.tiles_per_seg - 1 && p.size_out && goff + tot <= p.out_cap) p.size_out[v.g] = goff + tot;
         if (fatal_error(ws.ctrl)) *abort = 1;
         HC_PH(11);
       }
@@ -497,8 +498,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
         my_g = v.g;
         my_word = flag_pack(p.ring_epoch, ok ? goff : kFlagOffsetMask);
       }
-      // with sparse tiles this warp has nothing else to do: announce whatever has been stored
-      if (stored - flagged >= (p.sparse ? 1u : kFlagBatch)) raise_flags(stored);
+      if (stored - flagged >= kFlagBatch) raise_flags(stored);
     }
   } else {
     // ================================ compute warps ==============================================

@@ -521,7 +521,10 @@ extern "C" int hc_allreduce_host(hc_comm* c, const float* h_sbuf, float* h_rbuf,
                                  hc_stream_t stream) {
   if (!c || !h_sbuf || !h_rbuf || !(eb > 0.0f) || count > c->max_count) return hc::kErrArgument;
   if (count == 0) return hc::kOk;
-  if (pieces < 1) pieces = 8;
+  if (pieces < 1) {  // default: pieces of 4 MiB, at most 16 (fill and drain of the pipeline cost one piece each)
+    const size_t want = count / ((size_t)1 << 20);
+    pieces = want < 1 ? 1 : (want > 16 ? 16 : (int)want);
+  }
   if (pieces > kMaxHostPieces) pieces = kMaxHostPieces;
   if (!c->host_in) {  // first use: staging buffers, streams and events (set-up, not the call path)
     const size_t bytes = c->max_count * sizeof(float);

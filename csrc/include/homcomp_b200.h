@@ -136,7 +136,7 @@ int hc_comm_status(hc_comm* c, int clear);  // synchronises; sticky hc::Status
 // allocates or synchronises.
 int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, float eb, hc_stream_t stream);
 // The same sum for buffers in (pinned) host memory: the message crosses PCIe in `pieces` pieces
-// (0 = default 8, at most 32) on two copy streams of the handle while earlier pieces are reduced on
+// (0 = default: pieces of 4 MiB, at most 16; never more than 32) on two copy streams of the handle while earlier pieces are reduced on
 // `stream` and still earlier ones travel back, so the call costs about one direction of the
 // transfer.  `stream` ends behind the last copy down.  The first call allocates the device staging
 // (2 x max_count floats).  Pageable host memory works but serialises the copies.
@@ -212,6 +212,23 @@ int hc_comm_set_host_transport(hc_comm* c, const hc_host_transport* t);
 int hc_comm_allreduce_host_staged(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, float eb,
                                   hc_stream_t stream);
 
+// Symmetric regions with an NVSwitch multicast alias, built with the driver's virtual memory API
+// (cuMemCreate / cuMulticastCreate / AddDevice / BindMem): what hc_comm_create takes as peer_bases
+// and mc_base when the reduced chunks should leave with one multimem.st for all ranks and the
+// uncompressed sum should be formed inside the switch.  hc_mc_create_local: one process drives all
+// GPUs.  hc_mc_create_shared: one process per GPU (its current device); collective over `world`
+// ranks that pass the same `session` string, handles travel as file descriptors over a unix-domain
+// socket with rank 0 as the hub.  Regions come back zeroed.  Where a GPU lacks multicast support the
+// regions are still mapped on every GPU and hc_mc_multicast_ptr returns NULL (peer stores then).
+// All ranks must call hc_mc_destroy together, after a barrier of their own.
+typedef struct hc_mc_region hc_mc_region;
+int hc_multicast_supported(int device);
+int hc_mc_create_local(hc_mc_region** out, int n_dev, const int* devices, size_t bytes);
+int hc_mc_create_shared(hc_mc_region** out, int rank, int world, size_t bytes, const char* session);
+void* hc_mc_unicast_ptr(hc_mc_region* r, int idx);  // region of GPU / rank idx as addressable from here
+void* hc_mc_multicast_ptr(hc_mc_region* r);         // multimem instructions only; NULL without multicast
+size_t hc_mc_bytes(hc_mc_region* r);
+void hc_mc_destroy(hc_mc_region* r);
 // CUDA IPC helpers for the multi-process bootstrap (the 64-byte handle travels over any host
 // channel: torch.distributed, MPI, a file)
 int hc_ipc_alloc(void** d_ptr, size_t bytes, uint8_t handle[64]);

@@ -90,7 +90,7 @@ def test_uncompressed_and_named_variants():
     run_ranks(_raw_worker, 2)
 
 
-def _nvls_worker(rank, world, counts, eb, note_path):
+def _nvls_worker(rank, world, counts, eb, note_path, transport="nvls"):
     """Same check over the multicast transport.  Mismatches are collected and raised only after
     every rank has left the collective and unmapped its region together."""
     import torch.distributed as dist
@@ -99,7 +99,7 @@ def _nvls_worker(rank, world, counts, eb, note_path):
     from tirocinio_triennale_b200 import ops
     from tirocinio_triennale_b200.parallel import CompressedAllreduce
 
-    ar = CompressedAllreduce(max(counts), timeout_ms=5000, transport="nvls")
+    ar = CompressedAllreduce(max(counts), timeout_ms=5000, transport=transport)
     problems = []
     for algorithm in ("direct", "ring"):
         ar.set_algorithm(algorithm)
@@ -138,13 +138,17 @@ def _nvls_worker(rank, world, counts, eb, note_path):
     assert not problems, problems
 
 
-def test_allreduce_over_multicast_transport(tmp_path):
+@pytest.mark.parametrize("transport", ["nvls", "mc"])
+def test_allreduce_over_multicast_transport(tmp_path, transport):
+    """``nvls``: region and multicast mapping from torch's symmetric memory; ``mc``: from the library's
+    own bootstrap (driver virtual-memory API, file descriptors over a unix socket)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     world = min(torch.cuda.device_count(), 8)
     world = 1 << (world.bit_length() - 1)
     note = tmp_path / "multicast"
-    run_ranks(_nvls_worker, world, args=([1, 4097, 100000, (1 << 22) + 12345], 1e-4, str(note)), backend="nccl")
+    run_ranks(_nvls_worker, world, args=([1, 4097, 100000, (1 << 22) + 12345], 1e-4, str(note), transport),
+              backend="nccl")
     if note.read_text() != "1":
         pytest.skip("the fabric offers no multicast mapping: ran over peer stores on symmetric memory")
 

@@ -39,3 +39,10 @@ def test_allreduce_threads_tool():
     r = subprocess.run([str(exe), str(n), "2000000", "1e-4", "3"], capture_output=True, text=True, timeout=180)
     assert r.returncode == 0, r.stdout + r.stderr
     assert r.stdout.strip().endswith("ok")
+    # the same run over regions built by the library's own multicast bootstrap (driver VMM API): the
+    # compressed result must be the same bits (the line carries a checksum of rank 0's output)
+    m = subprocess.run([str(exe), str(n), "2000000", "1e-4", "3", "nvls"], capture_output=True, text=True, timeout=180)
+    assert m.returncode == 0, m.stdout + m.stderr
+    assert m.stdout.strip().endswith("ok")
+    checksum = lambda text: text.split("checksum")[1].split()[0]
+    assert checksum(m.stdout) == checksum(r.stdout)

@@ -22,7 +22,7 @@ OBJDIR = ROOT / "build" / "obj"
 
 CPU_SOURCES = ["cpu/hc_cpu_codec.cpp", "cpu/hc_cpu_ring.cpp"]
 CUDA_SOURCES = ["cuda/hc_kernels.cu", "cuda/hc_api.cu", "cuda/hc_ring.cu", "cuda/hc_compat.cu", "cuda/hc_noalloc.cu",
-                "cuda/hc_host_staged.cu"]
+                "cuda/hc_host_staged.cu", "cuda/hc_multicast.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-ffp-contract=off", "--fmad=false",

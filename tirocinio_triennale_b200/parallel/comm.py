@@ -25,17 +25,20 @@ class CompressedAllreduce:
     def __init__(self, max_count: int, group=None, device=None, timeout_ms: int | None = None,
                  algorithm: str = "direct", transport: str | None = None):
         """``transport``: ``"ipc"`` maps every rank's region with CUDA IPC and moves all data with peer
-        stores; ``"nvls"`` takes the region from ``torch.distributed._symmetric_memory`` and, where the
-        fabric offers a multicast mapping, pushes the reduced chunk to all ranks with one
-        ``multimem.st`` per 16 bytes (falls back to peer stores on the same mapping otherwise).
-        Default: the ``HC_TRANSPORT`` environment variable, else ``"ipc"``."""
+        stores.  ``"mc"`` builds the regions with the library's own bootstrap (``hc_mc_create_shared``:
+        driver virtual-memory API, handles passed as file descriptors over a unix socket) and, where
+        every GPU supports multicast, pushes the reduced chunk to all ranks with one ``multimem.st`` per
+        16 bytes and forms the uncompressed sum inside the switch (peer stores on the same mappings
+        otherwise).  ``"nvls"`` is the same data path on a region taken from
+        ``torch.distributed._symmetric_memory``.  Default: the ``HC_TRANSPORT`` environment variable,
+        else ``"ipc"``."""
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed must be initialised (it carries the IPC handles)")
         import os
 
         transport = transport or os.environ.get("HC_TRANSPORT", "ipc")
-        if transport not in ("ipc", "nvls"):
-            raise ValueError("transport must be 'ipc' or 'nvls'")
+        if transport not in ("ipc", "nvls", "mc"):
+            raise ValueError("transport must be 'ipc', 'mc' or 'nvls'")
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -46,6 +49,7 @@ class CompressedAllreduce:
         self._base = None
         self._h = None
         self._symm = None
+        self._mc_region = None
         self.multicast = False
         with torch.cuda.device(self.device):
             nbytes = int(self.lib.hc_comm_symmetric_bytes(self.world, self.max_count))
@@ -64,6 +68,30 @@ class CompressedAllreduce:
                     mc = C.c_void_p(int(hdl.multicast_ptr))
                     self.multicast = True
                 self._symm = (region, hdl)
+            elif transport == "mc" and self.world > 1:
+                import secrets
+
+                token = [("%d_%s" % (os.getpid(), secrets.token_hex(6))) if self.rank == 0 else None]
+                dist.broadcast_object_list(token, src=dist.get_global_rank(group, 0) if group is not None else 0,
+                                           group=group)
+                self.lib.hc_mc_create_shared.restype = C.c_int
+                self.lib.hc_mc_create_shared.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_size_t, C.c_char_p]
+                self.lib.hc_mc_unicast_ptr.restype = C.c_void_p
+                self.lib.hc_mc_unicast_ptr.argtypes = [C.c_void_p, C.c_int]
+                self.lib.hc_mc_multicast_ptr.restype = C.c_void_p
+                self.lib.hc_mc_multicast_ptr.argtypes = [C.c_void_p]
+                self.lib.hc_mc_destroy.restype = None
+                self.lib.hc_mc_destroy.argtypes = [C.c_void_p]
+                region = C.c_void_p()
+                _lib.check(self.lib.hc_mc_create_shared(C.byref(region), self.rank, self.world, nbytes,
+                                                        token[0].encode()), "mc_create_shared")
+                self._mc_region = region
+                for r in range(self.world):
+                    ptrs[r] = self.lib.hc_mc_unicast_ptr(region, r)
+                mcp = self.lib.hc_mc_multicast_ptr(region)
+                if mcp:
+                    mc = C.c_void_p(mcp)
+                    self.multicast = True
             else:
                 base = C.c_void_p()
                 handle = C.create_string_buffer(64)
@@ -106,9 +134,9 @@ class CompressedAllreduce:
         return recv
 
     def allreduce_host(self, send: torch.Tensor, recv: torch.Tensor | None = None, eb: float = 1e-4,
-                       pieces: int = 8) -> torch.Tensor:
+                       pieces: int = 0) -> torch.Tensor:
         """The same sum for float32 tensors in host memory (pin them: ``.pin_memory()``).  The message
-        crosses PCIe in ``pieces`` pieces while earlier pieces are being reduced and still earlier ones
+        crosses PCIe in ``pieces`` pieces (0: pieces of 4 MiB, at most 16) while earlier pieces are being reduced and still earlier ones
         travel back, so a call costs about one direction of the transfer.  Asynchronous: the result is
         on the host once the current CUDA stream has been synchronised."""
         if send.dtype != torch.float32 or send.is_cuda or not send.is_contiguous():
@@ -237,6 +265,9 @@ class CompressedAllreduce:
                 self.lib.hc_ipc_free(self._base)
             self._base = None
             self._symm = None
+            if self._mc_region is not None:
+                self.lib.hc_mc_destroy(self._mc_region)
+                self._mc_region = None
 
     def __del__(self):
         try:
