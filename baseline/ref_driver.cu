@@ -4,8 +4,10 @@
 #include <mpi.h>
 #include <stddef.h>
 
+#include "GSZ.h"
 #include "GSZ_entry.h"
 #include "cuda_awareallreduce.cuh"
+#include "homcomp.cuh"
 
 extern "C" {
 
@@ -39,6 +41,78 @@ size_t ref_hom_sum_F(unsigned char* d_in, float* d_local, unsigned char* d_out, 
   size_t sz = 0;
   homomorphic_sum_F(d_in, d_local, d_out, n, eb, &sz, in_size, 0);
   return sz;
+}
+
+// The reference's kernels alone, launched exactly as its host wrappers launch them
+// (HomComp/src/GSZ_entry.cu:285, :341, :534: grid = chunks of 32768 values, 32 threads, 8 bytes of
+// dynamic shared memory) but with the scratch arrays allocated once, as its `_opt` collective does
+// (HomComp/src/cuda_awareallreduce.cu:770-863), and their clearing outside the timed region: what is
+// left is the device time of GSZ_compress_kernel_outlier, GSZ_decompress_kernel_outlier and
+// kernel_homomophic_sum_F between two CUDA events.  ms[0..2] receive the medians over `iters` launches.
+// d_cmp / d_cmp2: buffers of at least n * 4 + n / 32 bytes; d_out: n floats.
+int ref_kernel_times(float* d_x, unsigned char* d_cmp, unsigned char* d_cmp2, float* d_out, size_t n, float eb, int iters,
+                     float* ms) {
+  const int bsize = cmp_tblock_size;
+  const int gsize = (int)((n + (size_t)bsize * cmp_chunk - 1) / ((size_t)bsize * cmp_chunk));
+  const size_t words = (size_t)gsize + 1;
+  unsigned int* scratch = nullptr;
+  if (cudaMalloc(&scratch, 6 * words * sizeof(unsigned int)) != cudaSuccess) return 1;
+  unsigned int *a = scratch, *b = a + words, *c = b + words, *d = c + words;
+  int *f1 = reinterpret_cast<int*>(d + words), *f2 = f1 + words;
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0);
+  cudaEventCreate(&e1);
+  const size_t rate_bytes = (n + (size_t)bsize * cmp_chunk - 1) / ((size_t)bsize * cmp_chunk) * ((size_t)bsize * cmp_chunk) / 32;
+  size_t cmp_size = 0;
+  int rc = 0;
+  if (iters < 1) iters = 1;
+  if (iters > 64) iters = 64;
+  float t[3][64];
+  for (int it = 0; it < iters + 2 && rc == 0; ++it) {
+    const int k = it >= 2 ? it - 2 : 0;  // two warm-up rounds land in slot 0 and are overwritten
+    float v = 0;
+    // compress
+    cudaMemset(scratch, 0, 6 * words * sizeof(unsigned int));
+    cudaEventRecord(e0);
+    GSZ_compress_kernel_outlier<<<gsize, bsize, sizeof(unsigned int) * 2>>>(d_x, d_cmp, a, b, f1, eb, n);
+    cudaEventRecord(e1);
+    if (cudaEventSynchronize(e1) != cudaSuccess) rc = 2;
+    cudaEventElapsedTime(&v, e0, e1);
+    t[0][k] = v;
+    unsigned int end = 0;
+    cudaMemcpy(&end, a + words - 2, sizeof(end), cudaMemcpyDeviceToHost);
+    cmp_size = (size_t)end + rate_bytes;
+    // decompress
+    cudaMemset(scratch, 0, 6 * words * sizeof(unsigned int));
+    cudaMemset(d_out, 0, n * sizeof(float));  // the reference decoder leaves zero blocks untouched
+    cudaEventRecord(e0);
+    GSZ_decompress_kernel_outlier<<<gsize, bsize, sizeof(unsigned int) * 2>>>(d_out, d_cmp, a, b, f1, eb, n, cmp_size);
+    cudaEventRecord(e1);
+    if (cudaEventSynchronize(e1) != cudaSuccess) rc = 2;
+    cudaEventElapsedTime(&v, e0, e1);
+    t[1][k] = v;
+    // fused homomorphic sum: stream (+) fp32 -> stream
+    cudaMemset(scratch, 0, 6 * words * sizeof(unsigned int));
+    cudaEventRecord(e0);
+    kernel_homomophic_sum_F<<<gsize, bsize, sizeof(unsigned int) * 2>>>(d_cmp, a, d_cmp2, b, c, d, f1, f2, d_x, eb, n, cmp_size);
+    cudaEventRecord(e1);
+    if (cudaEventSynchronize(e1) != cudaSuccess) rc = 2;
+    cudaEventElapsedTime(&v, e0, e1);
+    t[2][k] = v;
+  }
+  for (int q = 0; q < 3; ++q) {  // median
+    for (int i = 1; i < iters; ++i)
+      for (int j = i; j > 0 && t[q][j] < t[q][j - 1]; --j) {
+        const float tmp = t[q][j];
+        t[q][j] = t[q][j - 1];
+        t[q][j - 1] = tmp;
+      }
+    ms[q] = t[q][iters / 2];
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(scratch);
+  return cudaGetLastError() == cudaSuccess ? rc : 3;
 }
 
 }  // extern "C"
