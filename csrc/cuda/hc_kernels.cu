@@ -285,6 +285,10 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
   auto dst_first = [&](const Seg& v) -> uint32_t { return p.n_seg > 1 ? v.g : 0u; };
   auto dst_count = [&](const Seg&) -> uint32_t { return p.n_seg > 1 ? 1u : p.n_dst; };
 
+  if (tid == 32 && kHasLocal) {  // descriptor of the segment this CTA's first tile belongs to
+    const uint32_t g0 = p.n_seg > 1 ? blockIdx.x % p.n_seg : 0u;
+    if (p.use_tma[g0]) tma_prefetch_map(&tmaps.m[g0]);
+  }
   if (tid == 0) {
     for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(&sh.tma_full[i], 1);

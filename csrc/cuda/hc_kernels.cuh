@@ -569,17 +569,21 @@ __device__ __forceinline__ void copy_out(const uint8_t* obuf, uint8_t* const* ou
   const uint32_t nvec = (phase + tot + 15u) >> 4;
   const uint32_t sh = ((16u - phase) & 3u) * 8u;
   const uint32_t lo_valid = phase, hi_valid = phase + tot;
-  for (uint32_t v = t; v < nvec; v += nthr) {
+  auto fetch = [&](uint32_t v, uint32_t (&o)[4]) {  // the 16 bytes of unit v, shifted into place
     const int so = (int)(16u * v) - (int)phase;
     const uint32_t* wp = reinterpret_cast<const uint32_t*>(obuf + (so & ~3));
-    uint32_t w0 = wp[0], w1 = wp[1], w2 = wp[2], w3 = wp[3], w4 = sh ? wp[4] : 0u;
-    uint32_t o[4] = {__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh), __funnelshift_r(w2, w3, sh),
-                     __funnelshift_r(w3, w4, sh)};
+    const uint32_t w0 = wp[0], w1 = wp[1], w2 = wp[2], w3 = wp[3], w4 = sh ? wp[4] : 0u;
+    o[0] = __funnelshift_r(w0, w1, sh);
+    o[1] = __funnelshift_r(w1, w2, sh);
+    o[2] = __funnelshift_r(w2, w3, sh);
+    o[3] = __funnelshift_r(w3, w4, sh);
+  };
+  auto put = [&](uint32_t v, const uint32_t (&o)[4]) {
     const uint32_t lo = 16u * v, hi = lo + 16u;
     const bool full = lo >= lo_valid && hi <= hi_valid;
     if (full && mc != nullptr) {
       multimem_st_v4(mc + goff - phase + lo, o[0], o[1], o[2], o[3]);
-      continue;
+      return;
     }
 #pragma unroll 1
     for (uint32_t d = 0; d < n_dst; ++d) {
@@ -592,6 +596,11 @@ __device__ __forceinline__ void copy_out(const uint8_t* obuf, uint8_t* const* ou
           if (lo + b >= lo_valid && lo + b < hi_valid) p[b] = (uint8_t)(o[b >> 2] >> (8 * (b & 3)));
       }
     }
+  };
+  for (uint32_t v = t; v < nvec; v += nthr) {
+    uint32_t a[4];
+    fetch(v, a);
+    put(v, a);
   }
 }
 

@@ -88,7 +88,10 @@ def cpu():
     global _cpu
     with _lock:
         if _cpu is None:
-            path = _build.build_cpu()
+            import os
+
+            # HC_CPU_LIB: load this build of the portable library instead (e.g. one compiled with sanitizers)
+            path = os.environ.get("HC_CPU_LIB") or _build.build_cpu()
             lib = C.CDLL(str(path))
             _declare_cpu(lib)
             _cpu = lib

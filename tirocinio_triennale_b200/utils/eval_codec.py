@@ -47,7 +47,9 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--ops", default="compress,decompress,hom_add,doc",
-                    help="comma list of compress,decompress,hom_add,doc")
+                    help="comma list of compress,decompress,hom_add,doc,scatter7,reduce7 (the last two: the shapes "
+                         "of an 8-rank allreduce on one GPU: 7-segment compress of 7/8 of the data, 7 streams (+) "
+                         "fp32 of 1/8 of it)")
     args = ap.parse_args(argv)
 
     x = make_data(args)
@@ -89,6 +91,17 @@ def main(argv=None):
             codec.compress(tmp, eb, args.mode, out=out2, size=size2)
 
         report("doc", doc, 4 * n * 5 + 2 * nbytes)
+    if "scatter7" in want or "reduce7" in want:
+        # what rank 0 of 8 does in the direct algorithm, without the peers: chunk = n / 8
+        chunk = n // 8 // 4096 * 4096
+        parts = [x[(k + 1) * chunk: (k + 2) * chunk] for k in range(7)]
+        if "scatter7" in want:
+            report("scatter7", lambda: codec.compress_batch(parts, eb, args.mode), 7 * 4 * chunk + 7 * nbytes // 8)
+        if "reduce7" in want:
+            outs, sizes = codec.compress_batch(parts, eb, args.mode)
+            nb = [int(v) for v in sizes.tolist()]
+            report("reduce7", lambda: codec.hom_add_multi(outs, x[:chunk], eb, args.mode, stream_bytes=nb),
+                   4 * chunk + 8 * nbytes // 8)
     res["status"] = codec.status()
     print(json.dumps(res))
     return res

@@ -17,7 +17,7 @@ import torch.distributed as dist
 
 from . import datagen, timing
 
-NVLINK_GBS = 770.0  # measured peer copy per direction on this pool
+NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction between two B200s on one NVSwitch (GB/s)
 
 
 def main(argv=None):
