@@ -770,6 +770,13 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
       const uint32_t lt = t / p.n_seg, sg = t - lt * p.n_seg;  // tickets go round the segments
       const DecSegment& seg = p.seg[sg];
       fw = 0;
+      // a segment shorter than the longest one of the launch has tickets past its own tiles: nothing to
+      // wait for and nothing to read there (its producer never raises those flags)
+      if ((uint64_t)lt * kTileBlocks >= rate_bytes(seg.n)) {
+#pragma unroll
+        for (int i = 0; i < kRatesPerLane; ++i) r[i] = 0u;
+        return true;
+      }
       if (seg.in_ready && (fw = flag_peek(seg.in_ready + lt, p.ring_epoch)) == 0) return false;
       loader_fetch_rates(seg.in, seg.in_size, lt, r);
       return true;
@@ -795,7 +802,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
       const uint32_t lt = tile / p.n_seg, sg = tile - lt * p.n_seg;
       const DecSegment& seg = p.seg[sg];
       bool usable = true;
-      if (!have) {
+      if (!have) {  // (tickets past the segment's own tiles always come back from try_fetch with `have`)
         fw = 0;
         if (seg.in_ready && (fw = flag_wait_warp(seg.in_ready + lt, p.ring_epoch, ws)) == 0) usable = false;
         if (usable) loader_fetch_rates(seg.in, seg.in_size, lt, rates);

@@ -205,11 +205,27 @@ int hc_comm_set_timeout_ms(hc_comm* c, unsigned ms) {
 
 int hc_comm_status(hc_comm* c, int clear) {
   if (!c) return hc::kErrArgument;
-  uint32_t ctrl[4] = {0, 0, 0, 0};
+  // words 0-3: status of the codec kernels (2) and the first wait that ran out (3); words 32-35: the
+  // counters and the status word (34) of the uncompressed / hierarchical kernels
+  uint32_t ctrl[36];
+  memset(ctrl, 0, sizeof(ctrl));
   if (cudaDeviceSynchronize() != cudaSuccess) return hc::kErrCuda;
   if (cudaMemcpy(ctrl, c->ws_mem, sizeof(ctrl), cudaMemcpyDeviceToHost) != cudaSuccess) return hc::kErrCuda;
-  if (clear && (ctrl[0] | ctrl[1] | ctrl[2])) cudaMemset(c->ws_mem, 0, 64);  // status and ticket counters
-  return (int)ctrl[2];
+  const uint32_t st = ctrl[2] > ctrl[34] ? ctrl[2] : ctrl[34];
+  if (clear && (ctrl[0] | ctrl[1] | ctrl[2] | ctrl[3] | ctrl[33] | ctrl[34])) {
+    cudaMemset(c->ws_mem, 0, 64);                                      // status and ticket counters
+    cudaMemset(static_cast<uint32_t*>(c->ws_mem) + 32, 0, 4 * sizeof(uint32_t));  // raw kernels' counter and status
+  }
+  return (int)st;
+}
+
+// after a status 3: which wait ran out first (codes of hc_codec_status_site); read before clearing
+int hc_comm_status_site(hc_comm* c) {
+  if (!c) return -1;
+  uint32_t ctrl[4] = {0, 0, 0, 0};
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpy(ctrl, c->ws_mem, sizeof(ctrl), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return (int)ctrl[3];
 }
 
 int hc_comm_last_stream_bytes(hc_comm* c, uint64_t* bytes, int n) {

@@ -130,7 +130,8 @@ size_t hc_comm_symmetric_bytes(int world, size_t max_count);
 int hc_comm_create(hc_comm** out, int rank, int world, size_t max_count, void* const* peer_bases, void* mc_base);
 void hc_comm_destroy(hc_comm* c);
 int hc_comm_set_timeout_ms(hc_comm* c, unsigned ms);
-int hc_comm_status(hc_comm* c, int clear);  // synchronises; sticky hc::Status
+int hc_comm_status(hc_comm* c, int clear);  // synchronises; sticky hc::Status of all the handle's kernels
+int hc_comm_status_site(hc_comm* c);        // after a time-out: the wait that ran out first (see hc_codec_status_site)
 // Sum of `count` floats over all ranks, error at most world * eb per value; d_sbuf and d_rbuf may
 // alias.  Enqueues 3 kernels (direct algorithm, the default) or world + 1 (ring) on `stream`; never
 // allocates or synchronises.

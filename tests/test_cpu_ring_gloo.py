@@ -72,3 +72,28 @@ def _faulty_entry(rank, world):
                             init_method="tcp://127.0.0.1:%d" % (int(os.environ["MASTER_PORT"]) + 1),
                             timeout=datetime.timedelta(seconds=5))
     _faulty(rank, world)
+
+
+def test_hierarchy_oracle_composition():
+    """Host restatement of the hierarchical allreduce: one group is the plain fp32 sum in rank order; with
+    two groups every value is within (groups * eb) of the exact sum and every slice is what the compressed
+    ring gives for the group sums."""
+    import numpy as np
+
+    from tirocinio_triennale_b200 import ops
+    from tirocinio_triennale_b200.parallel import collectives
+
+    rng = np.random.default_rng(3)
+    n, eb = 10_007, 1e-4
+    bufs = [rng.normal(0, 0.01, n).astype(np.float32) for _ in range(4)]
+    one = collectives.hierarchy_oracle(bufs, 4, eb)
+    acc = np.zeros(n, np.float32)
+    for b in bufs:
+        acc = acc + b
+    np.testing.assert_array_equal(one, acc)
+    two = collectives.hierarchy_oracle(bufs, 2, eb)
+    exact = np.sum(np.stack(bufs).astype(np.float64), axis=0)
+    assert np.abs(two - exact).max() <= 2 * eb * 1.01 + 1e-6
+    B = ops.chunk_elems(n, 2)
+    s0, s1 = bufs[0] + bufs[1], bufs[2] + bufs[3]
+    np.testing.assert_array_equal(two[:B], ops.cpu_ring_allreduce([s0[:B], s1[:B]], eb)[0])

@@ -35,6 +35,25 @@ def _worker(rank, world, counts, eb, algorithm="direct"):
         ar.allreduce(y, None, eb)
         ar.set_overlap(True)
         np.testing.assert_array_equal(y.cpu().numpy(), want)
+        if algorithm == "direct" and it >= 3:
+            # packed transport buffers instead of tiles at fixed offsets, and the steps sharing the GPU
+            ar.set_sparse_tiles(False)
+            ar.set_shares(2, 1, 0)
+            z = torch.full_like(x, 5.0)
+            ar.allreduce(x, z, eb)
+            ar.set_sparse_tiles(True)
+            ar.set_shares(0, 0, 0)
+            assert ar.status() == 0
+            np.testing.assert_array_equal(z.cpu().numpy(), want)
+            # host buffers in, host buffers out: same values, whatever the number of pieces
+            hx = x.cpu().pin_memory()
+            for pieces in (0, 1, 3):
+                hy = torch.empty_like(hx).pin_memory()
+                ar.allreduce_host(hx, hy, eb, pieces=pieces)
+                torch.cuda.current_stream().synchronize()
+                assert ar.status() == 0
+                np.testing.assert_array_equal(hy.numpy(), want)
+    ar.allreduce(x, out, eb)  # so that the statistics below are those of a device-buffer call
     sizes = ar.last_stream_bytes()
     assert all(s > 0 for s in sizes)
     st = ar.stats()
@@ -49,7 +68,9 @@ def _worker(rank, world, counts, eb, algorithm="direct"):
 def test_allreduce_matches_host_oracle(world, algorithm):
     if torch.cuda.device_count() < world:
         pytest.skip("needs %d GPUs" % world)
-    counts = [1, 33, 4097, 100000, 1 << 20, (1 << 22) + 12345]
+    # 1048589: at 2 ranks the chunks are 524320 and 524269 values, one 32768-value chunk apart in their
+    # rate bytes, so the shorter stream has tile tickets past its own end in the shared decode launch
+    counts = [1, 33, 4097, 100000, 1 << 20, 1048589, (1 << 22) + 12345]
     run_ranks(_worker, world, args=(counts, 1e-4, algorithm))
 
 

@@ -23,6 +23,7 @@ def declare(lib):
         "hc_comm_create": [C.POINTER(vp), i, i, sz, C.POINTER(vp), vp],
         "hc_comm_set_timeout_ms": [vp, u],
         "hc_comm_status": [vp, i],
+        "hc_comm_status_site": [vp],
         "hc_allreduce": [vp, vp, vp, sz, f, vp],
         "hc_allreduce_raw": [vp, vp, vp, sz, vp],
         "hc_allreduce_mixed": [vp, vp, vp, vp, sz, f, vp],

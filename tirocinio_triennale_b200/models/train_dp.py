@@ -82,6 +82,7 @@ def run(args, compressed: bool, rank: int, world: int, device):
             out["compressed_checkpoint"] = stream_io.save_state("%s.%s.hcz" % (args.save, arm), model.state_dict(),
                                                                 args.save_compressed_eb)
     if state is not None:
+        state.check()  # a time-out or a missing peer in any bucket's collective surfaces here, not as silent garbage
         out["hook_calls"] = state.calls
         out["compressed_calls"] = state.compressed_calls
         state.close()

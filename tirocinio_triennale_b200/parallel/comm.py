@@ -185,6 +185,11 @@ class CompressedAllreduce:
         dist.barrier(group=self.group)
         return st
 
+    def status_site(self) -> int:
+        """After a time-out (status 3): code of the wait that ran out first; call before clearing."""
+        with torch.cuda.device(self.device):
+            return int(self.lib.hc_comm_status_site(self._h))
+
     def set_algorithm(self, algorithm: str):
         """``"ring"``: one fused kernel per reduce-scatter hop (world + 1 launches, the reference's
         algorithm); ``"direct"``: scatter, reduce, gather in three launches (default).  Same bits."""
