@@ -36,6 +36,7 @@ NBUF = 4  # rotating input/output sets: 4 x 64 MiB in + 4 x 64 MiB out > 126 MB 
 # Reference's published time for this message size (thesis Fig. 7.2 left, 32 x A100 over InfiniBand,
 # linear interpolation between the 40 MB and 80 MB bars): 0.0943 s -> 0.71 GB/s per rank.
 PUBLISHED_PER_RANK_GBS = 0.71
+AFFINITY = ""
 
 
 def _free_port():
@@ -55,6 +56,11 @@ def init_dist(n_gpus: int):
     if world != n_gpus:
         raise SystemExit("bench.py: --gpus %d but WORLD_SIZE=%d (launch with torch.distributed.run)" % (n_gpus, world))
     torch.cuda.set_device(local)
+    # host threads (and the pinned buffers they allocate) next to the GPU's PCIe root: both arms
+    from tirocinio_triennale_b200.utils import timing
+
+    global AFFINITY
+    AFFINITY = timing.bind_host_thread_near_gpu(local)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
     return rank, world, local
 
@@ -212,7 +218,7 @@ def run_ours(args, rank, world, local):
                 "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": 4 * COUNT, "d2h_bytes_per_step": 4 * COUNT},
         "gpu_launches": args.steps * (3 if world > 1 else 2),  # scatter-compress, reduce, decode per call and rank
         "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
-        "hbm_peak_gbs": peaks["hbm_gbs"], "peaks": peaks["source"],
+        "hbm_peak_gbs": peaks["hbm_gbs"], "peaks": peaks["source"], "host_affinity_rank0": AFFINITY,
     }
     return out
 

@@ -112,3 +112,30 @@ class ClockSampler:
         if sm:
             out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
         return out
+
+
+def bind_host_thread_near_gpu(device_index: int) -> str:
+    """Pins the calling process to the CPUs of the NUMA node that the GPU hangs off (sysfs
+    ``local_cpulist`` of its PCI device), so that pinned host buffers allocated afterwards are local to
+    the GPU's PCIe root and the copy engines do not cross the socket interconnect.  Returns a short
+    description of what was done; never raises (containers may hide sysfs)."""
+    try:
+        props = torch.cuda.get_device_properties(device_index)
+        addr = "%04x:%02x:%02x.0" % (getattr(props, "pci_domain_id", 0), props.pci_bus_id, props.pci_device_id)
+        base = Path("/sys/bus/pci/devices") / addr
+        cpus = (base / "local_cpulist").read_text().strip()
+        node = (base / "numa_node").read_text().strip()
+        ids = set()
+        for part in cpus.split(","):
+            if "-" in part:
+                a, b = part.split("-")
+                ids.update(range(int(a), int(b) + 1))
+            elif part:
+                ids.add(int(part))
+        allowed = ids & set(os.sched_getaffinity(0))
+        if not allowed:
+            return "gpu %d: numa node %s, no allowed cpu in %s" % (device_index, node, cpus)
+        os.sched_setaffinity(0, allowed)
+        return "gpu %d: numa node %s, bound to %d cpus" % (device_index, node, len(allowed))
+    except Exception as e:  # noqa: BLE001
+        return "gpu %d: not bound (%s)" % (device_index, str(e)[:80])
