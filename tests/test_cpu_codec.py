@@ -109,3 +109,12 @@ def test_cpu_ring_allreduce(P):
     qsum = sum(ops.cpu_quantize(b, eb).astype(np.int64) for b in bufs).astype(np.int32)
     np.testing.assert_array_equal(outs[0], ops.cpu_dequantize(qsum, eb))
     assert (hops > 0).all()
+
+
+def test_host_affinity_helper_never_raises():
+    """Used by bench.py before pinned buffers are allocated; on a machine without a GPU (or without the
+    sysfs entries) it must say so instead of failing."""
+    from tirocinio_triennale_b200.utils import timing
+
+    msg = timing.bind_host_thread_near_gpu(0)
+    assert isinstance(msg, str) and msg.startswith("gpu 0")
