@@ -328,18 +328,6 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       t = __shfl_sync(0xffffffffu, t, 0);
       return t < p.n_tiles ? t : kNoTile;
     };
-    // the same in two halves, so that the atomic's round trip overlaps the rest of the loader's turn:
-    // the ticket is only needed when the turn ends
-    auto take_issue = [&](bool wanted) -> uint32_t {  // lane 0: raw counter value (or kNoTile)
-      uint32_t t = kNoTile;
-      if (wanted && lane == 0 && !*abort) t = atomicAdd(ws.tick, 1u);
-      return t;
-    };
-    auto take_get = [&](uint32_t raw) -> uint32_t {
-      uint32_t t = __shfl_sync(0xffffffffu, raw, 0);
-      if (t != kNoTile) t += gridDim.x;
-      return t < p.n_tiles ? t : kNoTile;
-    };
     // non-blocking; fw receives the tile's arrival flag word when the stream has flags
     auto try_fetch = [&](uint32_t t, uint32_t q, uint32_t (&r)[kRatesPerLane], uint64_t& fw) -> bool {
       if (!kHasIn || t == kNoTile) return false;
@@ -356,7 +344,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
     bool have = try_fetch(tile, 0, rates, fw), have_n = false;
     for (uint32_t k = 0;; ++k) {
       const int s = k % NS, slot = k & 7;
-      const uint32_t tile_nn_raw = take_issue(tile != kNoTile && tile_n != kNoTile);
+      const uint32_t tile_nn = (tile != kNoTile && tile_n != kNoTile) ? take() : kNoTile;
       // staging job q of this tile (input stream q -> buffer (k * Q + q) & 1)
       auto stage_job = [&](uint32_t q) {
         const uint64_t nrate = rate_bytes(p.n[0]);
@@ -433,7 +421,7 @@ hc_encode_kernel(const __grid_constant__ TensorMaps tmaps, const EncParams p) {
       if (kHasIn)
         for (uint32_t q = before; q < Q; ++q) stage_job(q);
       tile = tile_n;
-      tile_n = take_get(tile_nn_raw);
+      tile_n = tile_nn;
     }
     if (lane == 0) HC_STAMP(6);
   } else if (warp == kComputeThreads / 32 + 1) {
@@ -776,18 +764,6 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
       t = __shfl_sync(0xffffffffu, t, 0);
       return t < p.n_tiles ? t : kNoTile;
     };
-    // the same in two halves, so that the atomic's round trip overlaps the rest of the loader's turn:
-    // the ticket is only needed when the turn ends
-    auto take_issue = [&](bool wanted) -> uint32_t {  // lane 0: raw counter value (or kNoTile)
-      uint32_t t = kNoTile;
-      if (wanted && lane == 0 && !*abort) t = atomicAdd(ws.tick, 1u);
-      return t;
-    };
-    auto take_get = [&](uint32_t raw) -> uint32_t {
-      uint32_t t = __shfl_sync(0xffffffffu, raw, 0);
-      if (t != kNoTile) t += gridDim.x;
-      return t < p.n_tiles ? t : kNoTile;
-    };
     // non-blocking; fw receives the tile's arrival flag word when the segment has flags
     auto try_fetch = [&](uint32_t t, uint32_t (&r)[kRatesPerLane], uint64_t& fw) -> bool {
       if (t == kNoTile) return false;
@@ -821,7 +797,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
         if (lane == 0) mbar_arrive(&sh.in_full[s]);
         break;
       }
-      const uint32_t tile_nn_raw = take_issue(tile_n != kNoTile);
+      const uint32_t tile_nn = tile_n != kNoTile ? take() : kNoTile;
       have_n = try_fetch(tile_n, rates_n, fw_n);
       const uint32_t lt = tile / p.n_seg, sg = tile - lt * p.n_seg;
       const DecSegment& seg = p.seg[sg];
@@ -840,7 +816,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
                           abort, flagged_in, fw & kFlagOffsetMask);
       if (lane == 0 && fatal_error(ws.ctrl)) *abort = 1;
       tile = tile_n;
-      tile_n = take_get(tile_nn_raw);
+      tile_n = tile_nn;
       have = have_n;
       fw = fw_n;
 #pragma unroll
