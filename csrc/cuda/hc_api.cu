@@ -7,6 +7,8 @@
 #include "hc_launch.h"
 #include "homcomp_b200.h"
 
+void hc_host_staged_release(const hc_codec* codec);  // hc_host_staged.cu
+
 struct hc_codec {
   void* ws_mem = nullptr;
   size_t ws_bytes = 0;
@@ -137,6 +139,7 @@ int hc_codec_create(hc_codec** out, size_t max_elems) {
 
 void hc_codec_destroy(hc_codec* c) {
   if (!c) return;
+  hc_host_staged_release(c);  // bounce buffers of the host-staged allreduce, if this handle ever ran it
   if (c->owns) cudaFree(c->ws_mem);
   delete c;
 }

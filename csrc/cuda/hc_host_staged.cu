@@ -7,11 +7,14 @@
 // HomComp/src/nca_allreduce.cu:195-324), which do the same around MPI_Send / MPI_Recv.  Partition,
 // hop order and arithmetic are those of the device ring and of hc_cpu_ring_allreduce, so the three
 // produce the same bits.  Like the reference's version it synchronises the host once per hop (the
-// message length has to be known on the host) and allocates its bounce buffers per call.
+// message length has to be known on the host); unlike it, the bounce buffers (two device, three
+// pinned) are kept per codec handle between calls and only grow.
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <string.h>
 
+#include <map>
+#include <mutex>
 
 #include "hc_format.h"
 #include "homcomp_b200.h"
@@ -25,6 +28,7 @@ struct Buffers {
   uint8_t* h_out = nullptr;  // pinned: what this rank sends
   uint8_t* h_in = nullptr;   // pinned: what this rank receives
   uint64_t* h_size = nullptr;
+  size_t cap = 0;
   ~Buffers() {
     if (d_in) cudaFree(d_in);
     if (d_out) cudaFree(d_out);
@@ -35,7 +39,42 @@ struct Buffers {
   }
 };
 
+// bounce buffers of every codec handle that has used this path; released by hc_codec_destroy
+std::map<const hc_codec*, Buffers*> g_buffers;
+std::mutex g_buffers_mu;
+
+Buffers* buffers_for(const hc_codec* codec, size_t cap) {
+  std::lock_guard<std::mutex> lock(g_buffers_mu);
+  Buffers*& b = g_buffers[codec];
+  if (b && b->cap >= cap) return b;
+  if (b) {
+    cudaDeviceSynchronize();
+    delete b;
+    b = nullptr;
+  }
+  Buffers* n = new Buffers();
+  if (cudaMalloc(&n->d_in, cap) != cudaSuccess || cudaMalloc(&n->d_out, cap) != cudaSuccess ||
+      cudaMalloc(&n->d_size, sizeof(uint64_t)) != cudaSuccess || cudaMallocHost(&n->h_out, cap) != cudaSuccess ||
+      cudaMallocHost(&n->h_in, cap) != cudaSuccess || cudaMallocHost(&n->h_size, sizeof(uint64_t)) != cudaSuccess) {
+    delete n;
+    g_buffers.erase(codec);
+    return nullptr;
+  }
+  n->cap = cap;
+  b = n;
+  return b;
+}
+
 }  // namespace
+
+// called by hc_codec_destroy
+void hc_host_staged_release(const hc_codec* codec) {
+  std::lock_guard<std::mutex> lock(g_buffers_mu);
+  auto it = g_buffers.find(codec);
+  if (it == g_buffers.end()) return;
+  delete it->second;
+  g_buffers.erase(it);
+}
 
 extern "C" int hc_allreduce_host_staged(hc_codec* codec, const hc_host_transport* t, int rank, int world,
                                         const float* d_sbuf, float* d_rbuf, size_t count, float eb, hc_stream_t stream) {
@@ -52,11 +91,9 @@ extern "C" int hc_allreduce_host_staged(hc_codec* codec, const hc_host_transport
     return (hi > count ? count : hi) - lo;
   };
   const size_t cap = hc_max_compressed_bytes(B) + 64;  // + what a bulk copy may read past the end
-  Buffers b;
-  if (cudaMalloc(&b.d_in, cap) != cudaSuccess || cudaMalloc(&b.d_out, cap) != cudaSuccess ||
-      cudaMalloc(&b.d_size, sizeof(uint64_t)) != cudaSuccess || cudaMallocHost(&b.h_out, cap) != cudaSuccess ||
-      cudaMallocHost(&b.h_in, cap) != cudaSuccess || cudaMallocHost(&b.h_size, sizeof(uint64_t)) != cudaSuccess)
-    return hc::kErrCuda;
+  Buffers* kept = buffers_for(codec, cap);  // allocated on the handle's first call (or when a larger one comes)
+  if (!kept) return hc::kErrCuda;
+  Buffers& b = *kept;
   if (cudaMemsetAsync(b.d_in, 0, cap, stream) != cudaSuccess) return hc::kErrCuda;
   const int next = (r + 1) % P, prev = (r - 1 + P) % P;
 

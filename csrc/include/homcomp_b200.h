@@ -196,8 +196,9 @@ int hc_comm_last_stream_bytes(hc_comm* c, uint64_t* bytes, int n);
 // memory and the caller's transport.  send/recv move one message to / from rank dst / src and
 // return 0 on success (recv stores the message length in *bytes; a message never exceeds cap).
 // Ranks with an even number send first, the others receive first, so a blocking transport is
-// fine.  Synchronises the host once per hop and allocates its bounce buffers per call, like the
-// reference's cpuCopy_* variants (HomComp/src/nca_allreduce.cu:195-324).  `codec` must have been
+// fine.  Synchronises the host once per hop, like the reference's cpuCopy_* variants
+// (HomComp/src/nca_allreduce.cu:195-324); its bounce buffers are allocated on the codec handle's first
+// call and kept (the reference allocates them per call).  `codec` must have been
 // created for at least hc_chunk_elems(count, world) values.
 typedef int (*hc_send_fn)(void* user, int dst, const void* buf, size_t bytes);
 typedef int (*hc_recv_fn)(void* user, int src, void* buf, size_t cap, size_t* bytes);

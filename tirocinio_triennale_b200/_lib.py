@@ -109,7 +109,9 @@ def cuda():
 
             tl = os.environ.get("HC_TIMELINE", "0") not in ("", "0")
             path = Path(_build.LIBDIR / ("libhomcomp_b200_tl.so" if tl else "libhomcomp_b200.so"))
-            if _build.nvcc_path() is not None:
+            if os.environ.get("HC_CUDA_LIB"):  # an alternative build of the library (debug, experiment)
+                path = Path(os.environ["HC_CUDA_LIB"])
+            elif _build.nvcc_path() is not None:
                 path = _build.build_cuda(timeline=tl)
             if not path.exists():
                 raise RuntimeError("libhomcomp_b200.so is missing and nvcc is not available to build it")
