@@ -235,6 +235,36 @@ int hc_decompress_flagged(hc_codec* c, const uint8_t* d_in, size_t in_size, size
 
 size_t hc_tile_elems(void) { return hc::kTileElems; }
 
+// Decode n_in streams of the same n values and add them in the quantised domain: d_x receives
+// (sum of the quantised values) * 2 eb, the result a chain of homomorphic adds followed by one
+// decompress would give, with one kernel and no intermediate stream.
+int hc_decompress_sum(hc_codec* c, int n_in, const uint8_t* const* d_in, const size_t* in_size, size_t n, float eb,
+                      float* d_x, hc_stream_t stream) {
+  if (int rc = check_call(c, n, eb, true)) return rc;
+  if (n_in < 1 || n_in > hc::kMaxDst || !d_in || !in_size || !d_x) return hc::kErrArgument;
+  if ((size_t)n_in * hc::rate_bytes(n) > hc::rate_bytes(c->max_elems) + 64) return hc::kErrArgument;
+  if (n == 0) return hc::kOk;
+  hc::DecParams p;
+  memset(&p, 0, sizeof(p));
+  p.n_seg = (uint32_t)n_in;
+  p.sum = 1;
+  for (int q = 0; q < n_in; ++q) {
+    p.seg[q].in = d_in[q];
+    p.seg[q].in_size = in_size[q];
+    p.seg[q].out = d_x;
+    p.seg[q].n = n;
+  }
+  p.eb = eb;
+  p.ws = next_workspace(c, stream);
+  const uint64_t* ready[hc::kMaxIn] = {};
+  const bool flagged = stage_offsets(c, p.ws, d_in, in_size, p.n_seg, n, ready, stream);
+  if (flagged) {
+    p.ring_epoch = p.ws.epoch;
+    for (int q = 0; q < n_in; ++q) p.seg[q].in_ready = ready[q];
+  }
+  return hc::launch_decode(hc::kModeOutlier, p, stream, flagged) == cudaSuccess ? hc::kOk : hc::kErrCuda;
+}
+
 // Several independent tensors compressed by one launch (segments); sizes land in d_sizes[g].
 int hc_compress_batch(hc_codec* c, int n_seg, const float* const* d_x, const size_t* n, float eb, int mode,
                       uint8_t* const* d_out, size_t cap_each, uint64_t* d_sizes, hc_stream_t stream) {

@@ -720,8 +720,11 @@ struct __align__(16) DecShared {
   uint8_t in_rate[2][kTileBlocks];
 };
 
-template <int MODE>
-__global__ void __launch_bounds__(kDecThreads, 4)
+// SUM: the n_seg streams hold contributions to ONE array (every rank's whole message in the one-step
+// form of the allreduce): a CTA stages tile lt of every stream in turn, adds the decoded quantised
+// values in registers and writes seg[0].out once per tile.  Tickets then count tiles, not (tile, stream).
+template <int MODE, bool SUM>
+__global__ void __launch_bounds__(kDecThreads, SUM ? 3 : 4)
 hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -758,11 +761,19 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
     // CTA i starts with tile i, later tiles come from the shared ticket counter.  Software pipeline
     // over this CTA's tiles: the ticket is taken two turns ahead and the rate bytes one turn ahead,
     // so neither round trip sits between two look-backs.
+    uint32_t handed = kNoTile, handed_sg = 0;  // SUM: the (tile, stream) pair handed out last
     auto take = [&]() -> uint32_t {  // lane 0 takes a ticket, every lane gets it
+      if (SUM && handed != kNoTile && handed_sg + 1 < p.n_seg) {
+        ++handed_sg;
+        return ++handed;  // the next stream of the same tile
+      }
       uint32_t t = kNoTile;
       if (lane == 0 && !*abort) t = gridDim.x + atomicAdd(ws.tick, 1u);
       t = __shfl_sync(0xffffffffu, t, 0);
-      return t < p.n_tiles ? t : kNoTile;
+      if (!SUM) return t < p.n_tiles ? t : kNoTile;
+      handed = t < p.tiles_per_seg ? t * p.n_seg : kNoTile;
+      handed_sg = 0;
+      return handed;
     };
     // non-blocking; fw receives the tile's arrival flag word when the segment has flags
     auto try_fetch = [&](uint32_t t, uint32_t (&r)[kRatesPerLane], uint64_t& fw) -> bool {
@@ -781,7 +792,8 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
       loader_fetch_rates(seg.in, seg.in_size, lt, r);
       return true;
     };
-    uint32_t tile = (!*abort && blockIdx.x < p.n_tiles) ? blockIdx.x : kNoTile;
+    uint32_t tile = (!*abort && blockIdx.x < (SUM ? p.tiles_per_seg : p.n_tiles)) ? blockIdx.x : kNoTile;
+    if (SUM && tile != kNoTile) tile = handed = tile * p.n_seg;
     if (lane == 0) HC_STAMP(1);
     uint32_t tile_n = tile != kNoTile ? take() : kNoTile;
     uint32_t rates[kRatesPerLane] = {}, rates_n[kRatesPerLane] = {};
@@ -826,6 +838,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
   } else {
     // ================================ compute warps ==============================================
     if (tid == 0) HC_PH_START();
+    int32_t acc[SUM ? 32 : 1];
     for (uint32_t k = 0;; ++k) {
       const int s = k & 1;
       bool alive = wait_or_flag(&sh.in_full[s], (k >> 1) & 1, ws, abort, kSiteDecodeInFull);
@@ -834,7 +847,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
       const uint32_t tile = alive ? sh.tile[k & 3] : kNoTile;
       if (tile == kNoTile) break;
       const uint32_t lt = tile / p.n_seg, sg = tile - lt * p.n_seg;
-      const DecSegment& seg = p.seg[sg];
+      const DecSegment& seg = p.seg[SUM ? 0u : sg];  // where the tile goes
       const bool tma = seg.use_tma != 0;
       const uint64_t full_rows = seg.n / kBlock;
       const uint32_t rate = sh.in_rate[s][tid];
@@ -849,6 +862,18 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
         for (int i = 0; i < 32; ++i) d[i] = 0;
       }
       mbar_arrive(&sh.in_free[s]);
+      if (SUM) {
+        if (sg == 0) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[i] = d[i];
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[i] += d[i];
+        }
+        if (sg + 1 < p.n_seg) continue;  // more streams of this tile to come
+#pragma unroll
+        for (int i = 0; i < 32; ++i) d[i] = acc[i];
+      }
       if (tid == 0) HC_PH(1);
       if (k == 0 && tid == 0) HC_STAMP(3);
       uint32_t w[32];
@@ -871,7 +896,7 @@ hc_decode_kernel(const __grid_constant__ TensorMaps tmaps, const DecParams p) {
         HC_PH(4);
         HC_PH_COUNT();
         if (tma && (uint64_t)lt * kTileBlocks < full_rows)
-          tma_store_2d(&tmaps.m[sg], 0, (int)(lt * kTileBlocks), obuf);
+          tma_store_2d(&tmaps.m[SUM ? 0u : sg], 0, (int)(lt * kTileBlocks), obuf);
         tma_commit_group();
         if (k == 0) HC_STAMP(5);
       }
@@ -1136,15 +1161,17 @@ cudaError_t launch_encode_m(int mode, const TensorMaps& map, const EncParams& p,
   }
 }
 
-template <int MODE>
+template <int MODE, bool SUM = false>
 cudaError_t launch_decode_t(const TensorMaps& maps, const DecParams& p, cudaStream_t stream, bool overlap) {
   static thread_local int cache[64] = {};
-  const int cap = resident_ctas(dev::hc_decode_kernel<MODE>, dev::kDecThreads, kDecSmem, cache);
+  const int cap = resident_ctas(dev::hc_decode_kernel<MODE, SUM>, dev::kDecThreads, kDecSmem, cache);
   if (cap <= 0) return cudaErrorLaunchOutOfResources;
-  int grid = (int)(p.n_tiles < (uint32_t)cap ? p.n_tiles : (uint32_t)cap);
+  const uint32_t tickets = SUM ? p.tiles_per_seg : p.n_tiles;
+  int grid = (int)(tickets < (uint32_t)cap ? tickets : (uint32_t)cap);
   if (p.grid_limit && (int)p.grid_limit < grid) grid = (int)p.grid_limit;
-  if (overlap) return launch_overlapped(dev::hc_decode_kernel<MODE>, grid, dev::kDecThreads, kDecSmem, stream, maps, p);
-  dev::hc_decode_kernel<MODE><<<grid, dev::kDecThreads, kDecSmem, stream>>>(maps, p);
+  if (overlap)
+    return launch_overlapped(dev::hc_decode_kernel<MODE, SUM>, grid, dev::kDecThreads, kDecSmem, stream, maps, p);
+  dev::hc_decode_kernel<MODE, SUM><<<grid, dev::kDecThreads, kDecSmem, stream>>>(maps, p);
   return cudaGetLastError();
 }
 
@@ -1234,6 +1261,14 @@ cudaError_t launch_decode(int mode, DecParams p, cudaStream_t stream, bool overl
   p.n_tiles = p.tiles_per_seg * p.n_seg;
   TensorMaps maps;
   memset(&maps, 0, sizeof(maps));
+  if (p.sum) {
+    // one output: every stream must describe the same array
+    for (uint32_t i = 1; i < p.n_seg; ++i)
+      if (p.seg[i].n != p.seg[0].n) return cudaErrorInvalidValue;
+    if (mode == kModeVec) return cudaErrorInvalidValue;
+    p.seg[0].use_tma = make_rows_map(&maps.m[0], p.seg[0].out, p.seg[0].n / kBlock) ? 1u : 0u;
+    return launch_decode_t<kModeOutlier, true>(maps, p, stream, overlap);
+  }
   for (uint32_t i = 0; i < p.n_seg; ++i)
     p.seg[i].use_tma = make_rows_map(&maps.m[i], p.seg[i].out, p.seg[i].n / kBlock) ? 1u : 0u;
   switch (mode) {
@@ -1291,7 +1326,7 @@ extern "C" int hc_resident_ctas(int op) {
     case 2: return hc::encode_capacity<hc::kOpAddF32, hc::kModeOutlier, true>();
     case 3: {
       static thread_local int cache[64] = {};
-      return hc::resident_ctas(hc::dev::hc_decode_kernel<hc::kModeOutlier>, hc::dev::kDecThreads, hc::kDecSmem, cache);
+      return hc::resident_ctas(hc::dev::hc_decode_kernel<hc::kModeOutlier, false>, hc::dev::kDecThreads, hc::kDecSmem, cache);
     }
     default: return 0;
   }

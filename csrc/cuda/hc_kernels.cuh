@@ -119,6 +119,8 @@ struct DecParams {
   uint32_t ring_epoch;
   float eb;
   uint32_t grid_limit;  // at most this many CTAs (0: as many as the GPU holds)
+  uint32_t sum;         // 1: the n_seg streams are contributions to one array of seg[0].n values; their
+                        //    quantised values are added tile by tile and seg[0].out receives the sum
   Workspace ws;
 };
 struct TensorMaps {

@@ -34,6 +34,7 @@ inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 struct Layout {
   int world = 0;
   size_t chunk_max = 0;   // elements per chunk at max_count
+  size_t slot_elems = 0;  // values whose stream one slot holds in the worst case
   size_t slot_bytes = 0;  // capacity of one stream slot
   size_t flag_bytes = 0;  // flags of one slot
   size_t n_slots = 0;
@@ -43,8 +44,11 @@ struct Layout {
   Layout(int P, size_t max_count) {
     world = P;
     chunk_max = hc_chunk_elems(max_count, P);
-    slot_bytes = round_up(hc::max_stream_bytes(chunk_max) + 64, kAlign);
-    flag_bytes = round_up((hc::rate_bytes(chunk_max) / hc::kTileBlocks + 1) * sizeof(uint64_t), kAlign);
+    // Two ranks: the one-step form moves as many bytes as the other two and has a phase less, so the
+    // slots hold a whole message there and every call can take it.
+    slot_elems = P == 2 ? (max_count > chunk_max ? max_count : chunk_max) : chunk_max;
+    slot_bytes = round_up(hc::max_stream_bytes(slot_elems) + 64, kAlign);
+    flag_bytes = round_up((hc::rate_bytes(slot_elems) / hc::kTileBlocks + 1) * sizeof(uint64_t), kAlign);
     n_slots = (size_t)(P - 1) + 2 * (size_t)P;
     flags_off = n_slots * slot_bytes;
     raw_flags_off = flags_off + n_slots * flag_bytes;
@@ -76,7 +80,8 @@ struct hc_comm {
   uint32_t ws_epoch = 0;
   uint32_t call = 0;
   uint32_t raw_call = 0;
-  int algorithm = 1;              // 0 ring (P + 1 kernels), 1 direct (3 kernels)
+  int algorithm = 1;              // 0 ring (P + 1 kernels), 1 direct (3 kernels), 2 one step (2 kernels) where it fits
+  size_t small_count = 0;         // direct: messages of at most this many values take the one-step form
   bool trace = false;             // record one CUDA event per step of hc_allreduce
   bool overlap = true;            // direct algorithm: steps 2 and 3 start while their predecessor drains
   int share_scatter = 0, share_reduce = 0;  // direct algorithm: quarters of the GPU for steps 1 and 2 (0: all of it)
@@ -458,8 +463,91 @@ static int allreduce_direct(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
   return hc::kOk;
 }
 
+// One-step form for messages that fit one all-gather slot (count <= max_count / world, rounded to the
+// chunk geometry), two kernels per call:
+//   1. compress the WHOLE local message once and push the stream to every rank's all-gather slot for
+//      this source (peer stores or one multimem store per unit; one arrival flag per tile);
+//   2. one decode that stages tile t of all P streams as their flags arrive, adds the quantised
+//      values in registers and writes the fp32 sum.
+// The sum of the ranks' quantised values is the same integer whatever the grouping, so the result
+// has the bits of the other two forms; what changes is one network phase instead of two and no
+// re-encoding, at the price of P-1 instead of 2 (P-1)/P messages on the wire: the form for small
+// messages, where a call is made of fixed costs.  Slots and flags are those of the all-gather phase
+// (set `call & 1`), and step 1 is a normal launch behind the previous call, so the argument for
+// reusing them without a reset is the one of the direct form.
+static int allreduce_onestep(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, float eb, hc_stream_t stream) {
+  const int P = c->world, r = c->rank;
+  const Layout& L = c->lay;
+  c->call += 1;
+  if ((c->call & 0xffffffu) == 0) c->call += 1;
+  const uint32_t call = c->call;
+  const int parity = (int)(call & 1u);
+  uint8_t* self = c->peer[r];
+  c->n_ev = 0;
+  auto mark = [&]() {
+    if (c->trace) cudaEventRecord(c->ev[c->n_ev++], stream);
+  };
+  const bool overlap = c->overlap && !c->trace;
+  mark();
+  {
+    NvtxRange step_range("hc one-step: compress + broadcast");
+    hc::EncParams p;
+    memset(&p, 0, sizeof(p));
+    p.n_seg = 1;
+    p.local[0] = d_sbuf;
+    p.n[0] = count;
+    p.recip = 0.5f / eb;
+    p.ring_epoch = call;
+    p.out_cap = L.slot_bytes;
+    p.size_out = c->sizes;
+    const size_t slot = L.ag_slot(parity, r);
+    p.n_dst = (uint32_t)P;
+    for (int k = 0; k < P; ++k) {
+      const int dst = (r + k) % P;
+      p.out[k] = c->peer[dst] + L.data_off(slot);
+      p.out_ready[k] = reinterpret_cast<uint64_t*>(c->peer[dst] + L.flag_off(slot));
+    }
+    if (c->mc && P > 1) p.out_mc = c->mc + L.data_off(slot);
+    p.sparse = c->sparse ? 1u : 0u;
+    p.ws = next_ws(c, stream);
+    if (hc::launch_encode(hc::kOpCompress, hc::kModeOutlier, p, stream) != cudaSuccess) return hc::kErrCuda;
+  }
+  mark();
+  NvtxRange decode_range("hc one-step: decode + sum");
+  hc::DecParams d;
+  memset(&d, 0, sizeof(d));
+  d.eb = eb;
+  d.ring_epoch = call;
+  d.sum = 1;
+  for (int k = 0; k < P; ++k) {
+    const int src = (r + k) % P;  // own stream first: it is stored locally
+    const size_t slot = L.ag_slot(parity, src);
+    hc::DecSegment& sg = d.seg[d.n_seg++];
+    sg.in = self + L.data_off(slot);
+    sg.in_size = L.slot_bytes;
+    sg.in_ready = reinterpret_cast<const uint64_t*>(self + L.flag_off(slot));
+    sg.out = d_rbuf;
+    sg.n = count;
+  }
+  d.ws = next_ws(c, stream);
+  if (hc::launch_decode(hc::kModeOutlier, d, stream, overlap) != cudaSuccess) return hc::kErrCuda;
+  mark();
+  // the other words of the size report belong to steps this form does not have
+  if (P > 1 && cudaMemsetAsync(c->sizes + 1, 0, (size_t)(P - 1) * sizeof(uint64_t), stream) != cudaSuccess) return hc::kErrCuda;
+  return hc::kOk;
+}
+
+// Largest count the one-step form can take: what one stream slot holds.
+static size_t onestep_capacity(const hc_comm* c) { return c->lay.slot_elems; }
+
+extern "C" int hc_comm_set_small_count(hc_comm* c, size_t count) {
+  if (!c) return hc::kErrArgument;
+  c->small_count = count;
+  return hc::kOk;
+}
+
 extern "C" int hc_comm_set_algorithm(hc_comm* c, int algorithm) {
-  if (!c || algorithm < 0 || algorithm > 1) return hc::kErrArgument;
+  if (!c || algorithm < 0 || algorithm > 2) return hc::kErrArgument;
   c->algorithm = algorithm;
   return hc::kOk;
 }
@@ -523,8 +611,11 @@ extern "C" int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
   if (!c || !d_sbuf || !d_rbuf || !(eb > 0.0f) || count > c->max_count) return hc::kErrArgument;
   if (count == 0) return hc::kOk;
   NvtxRange call_range("hc_allreduce");
-  return c->algorithm == 0 ? allreduce_ring(c, d_sbuf, d_rbuf, count, eb, stream)
-                           : allreduce_direct(c, d_sbuf, d_rbuf, count, eb, stream);
+  if (c->algorithm == 0) return allreduce_ring(c, d_sbuf, d_rbuf, count, eb, stream);
+  // one step for every message that fits (algorithm 2), or for those up to the small-message limit
+  if (c->world > 1 && count <= onestep_capacity(c) && (c->algorithm == 2 || count <= c->small_count))
+    return allreduce_onestep(c, d_sbuf, d_rbuf, count, eb, stream);
+  return allreduce_direct(c, d_sbuf, d_rbuf, count, eb, stream);
 }
 
 // Host buffers in, host buffers out.  The reference's hostptr entry points copy the whole input up,

@@ -95,6 +95,11 @@ int hc_decompress(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, fl
 int hc_decompress_flagged(hc_codec* c, const uint8_t* d_in, size_t in_size, size_t n, float eb, int mode, float* d_x,
                           const uint64_t* d_tile_flags, uint32_t want, hc_stream_t stream);
 size_t hc_tile_elems(void);
+// n_in (1..8) streams of the same n values, decoded and added in the quantised domain by one kernel:
+// d_x = (q_1 + ... + q_n_in) * 2 eb, the values a chain of homomorphic adds followed by hc_decompress
+// would give, without the intermediate streams.  Outlier / plain streams.
+int hc_decompress_sum(hc_codec* c, int n_in, const uint8_t* const* d_in, const size_t* in_size, size_t n, float eb,
+                      float* d_x, hc_stream_t stream);
 int hc_hom_add_f32(hc_codec* c, const uint8_t* d_in, size_t in_size, const float* d_local, size_t n, float eb,
                    int mode, uint8_t* d_out, size_t cap, uint64_t* d_size, hc_stream_t stream);
 // d_deltas: hc_quant_pred output, padded to whole 32-element blocks
@@ -146,7 +151,13 @@ int hc_allreduce_host(hc_comm* c, const float* h_sbuf, float* h_rbuf, size_t cou
 // algorithm 0: ring reduce-scatter with one fused kernel per hop (world + 1 launches);
 // algorithm 1 (default): direct scatter -> reduce -> gather for a switched fabric (3 launches).
 // Both produce byte-identical reduced streams, hence bit-identical results.
+// algorithm 2: one step (2 launches) for every message of at most max_count / world values (larger ones
+// take the direct form): every rank broadcasts its whole compressed message and decodes the sum of
+// all streams.  Same result bits again; world - 1 messages on the wire instead of 2 (world - 1) / world.
 int hc_comm_set_algorithm(hc_comm* c, int algorithm);
+// Direct algorithm: messages of at most `count` values (and at most max_count / world) take the
+// one-step form, which has one network phase less (default 0: never).
+int hc_comm_set_small_count(hc_comm* c, size_t count);
 // Direct algorithm: launch steps 2 and 3 with programmatic stream serialisation, so that each fills
 // the SMs while its predecessor drains (default on; off while tracing).  Same results either way.
 int hc_comm_set_overlap(hc_comm* c, int on);

@@ -74,6 +74,65 @@ def test_allreduce_matches_host_oracle(world, algorithm):
     run_ranks(_worker, world, args=(counts, 1e-4, algorithm))
 
 
+def _onestep_worker(rank, world, counts, eb):
+    import torch.distributed as dist
+
+    from datasets import gradient_like, smooth
+    from tirocinio_triennale_b200 import ops
+    from tirocinio_triennale_b200.parallel import CompressedAllreduce
+
+    max_count = world * (1 << 20)
+    ar = CompressedAllreduce(max_count, timeout_ms=5000, algorithm="onestep")
+    bad = []
+    for it, n in enumerate(counts):
+        gen = smooth if it % 2 == 0 else gradient_like
+        bufs = [gen(n, seed=300 * it + r) for r in range(world)]
+        want = ops.cpu_ring_allreduce(bufs, eb)[rank]
+        x = torch.from_numpy(bufs[rank]).cuda()
+        out = torch.full_like(x, -3.0)
+        ar.allreduce(x, out, eb)
+        if ar.status() != 0 or not np.array_equal(out.cpu().numpy(), want):
+            bad.append(("onestep", n))
+        # twice more in place: both sets of slots and flags are reused without a reset
+        y = x.clone()
+        ar.allreduce(y, None, eb)
+        z = x.clone()
+        ar.allreduce(z, None, eb)
+        if not (np.array_equal(y.cpu().numpy(), want) and np.array_equal(z.cpu().numpy(), want)):
+            bad.append(("onestep in place", n))
+    sizes = ar.last_stream_bytes()
+    if not (sizes[0] > 0 and all(s == 0 for s in sizes[1:])):
+        bad.append(("sizes", sizes))
+    # the direct form with a small-message limit: calls of both kinds share slots, flags and counters
+    ar.set_algorithm("direct")
+    ar.set_small_count(100_000)
+    for it, n in enumerate([4097, 200_000, 33, 150_000, 100_000]):
+        bufs = [gradient_like(n, seed=500 + 10 * it + r) for r in range(world)]
+        want = ops.cpu_ring_allreduce(bufs, eb)[rank]
+        x = torch.from_numpy(bufs[rank]).cuda()
+        ar.allreduce(x, None, eb)
+        if ar.status() != 0 or not np.array_equal(x.cpu().numpy(), want):
+            bad.append(("mixed", n))
+    # a message too large for one slot falls back to the direct form
+    ar.set_algorithm("onestep")
+    n = (1 << 20) + 4096 * world
+    bufs = [smooth(n, seed=700 + r) for r in range(world)]
+    x = torch.from_numpy(bufs[rank]).cuda()
+    ar.allreduce(x, None, eb)
+    if ar.status() != 0 or not np.array_equal(x.cpu().numpy(), ops.cpu_ring_allreduce(bufs, eb)[rank]):
+        bad.append(("fallback", n))
+    dist.barrier()
+    ar.close()
+    assert not bad, bad
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_one_step_allreduce_matches_host_oracle(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    run_ranks(_onestep_worker, world, args=([1, 33, 4097, 100000, 1 << 20], 1e-4))
+
+
 def _raw_worker(rank, world):
     import torch.distributed as dist
 

@@ -173,6 +173,27 @@ def test_multi_stream_add_matches_oracle(k, n):
     np.testing.assert_array_equal(_stream(out, size), want)
 
 
+@pytest.mark.parametrize("k", [1, 2, 4, 8])
+@pytest.mark.parametrize("n", [1, 33, 8193, 300000, 1100 * 4096 + 7])
+def test_decode_and_sum_of_streams_matches_oracle(k, n):
+    """One kernel decodes k streams and adds their quantised values: the oracle's chain of stream adds
+    followed by one decompress, bit for bit (1100 tiles and more go through the offsets pre-pass)."""
+    eb = 1e-4
+    codec = ops.Codec(max_elems=8 * n + 8 * 32768)  # room for eight look-back chains of whole chunks
+    xs = [ALL["gradient" if i % 2 else "smooth"](n, seed=40 + i) for i in range(k)]
+    streams = [ops.cpu_compress(x, eb) for x in xs]
+    acc = streams[0]
+    for s in streams[1:]:
+        acc = ops.cpu_hom_add_streams(acc, s, n)
+    want = ops.cpu_decompress(acc, n, eb)
+    gs = [_gpu(np.concatenate([s, np.zeros(32, np.uint8)])) for s in streams]
+    for _ in range(2):
+        out = torch.full((n,), -7.0, device="cuda")
+        codec.decompress_sum(gs, n, eb, out=out, stream_bytes=[s.size for s in streams])
+        assert codec.status() == 0
+        np.testing.assert_array_equal(out.cpu().numpy(), want)
+
+
 @pytest.mark.parametrize("k,n", [(1, 500 * 4096 + 77), (3, 520 * 4096), (7, 1000 * 4096 + 5)])
 def test_multi_stream_add_about_one_tile_per_cta(k, n):
     """Tile counts for which the launcher picks the single-stage, four-CTAs-per-SM variant of the

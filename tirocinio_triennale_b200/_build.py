@@ -81,6 +81,19 @@ def build_cuda(force: bool = False, verbose: bool = False, timeline: bool = Fals
     if nvcc is None:
         raise RuntimeError("nvcc not found; cannot build the sm_100a library")
     LIBDIR.mkdir(parents=True, exist_ok=True)
+    # the ranks of a job import the package at the same time: one of them builds, the others wait
+    # for it and find the library fresh (they share the object files, so two builds at once would
+    # link each other's half-written objects)
+    import fcntl
+
+    with open(LIBDIR / (".build_tl.lock" if timeline else ".build.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and not _stale(lib):
+            return lib
+        return _build_cuda_locked(lib, nvcc, verbose, timeline)
+
+
+def _build_cuda_locked(lib: Path, nvcc: str, verbose: bool, timeline: bool) -> Path:
     objdir = OBJDIR / "tl" if timeline else OBJDIR
     objdir.mkdir(parents=True, exist_ok=True)
     inc = ["-I", str(CSRC / "include"), "-I", str(CSRC / "cuda")]

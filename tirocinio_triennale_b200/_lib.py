@@ -70,6 +70,7 @@ def _declare_cuda(lib):
         "hc_compress": [vp, vp, sz, f, i, vp, sz, vp, vp],
         "hc_decompress": [vp, vp, sz, sz, f, i, vp, vp],
         "hc_decompress_flagged": [vp, vp, sz, sz, f, i, vp, vp, C.c_uint, vp],
+        "hc_decompress_sum": [vp, i, vp, vp, sz, f, vp, vp],
         "hc_hom_add_f32": [vp, vp, sz, vp, sz, f, i, vp, sz, vp, vp],
         "hc_hom_add_i32": [vp, vp, sz, vp, sz, i, vp, sz, vp, vp],
         "hc_hom_add_stream": [vp, vp, sz, vp, sz, sz, i, vp, sz, vp, vp],

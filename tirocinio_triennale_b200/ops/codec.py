@@ -163,6 +163,23 @@ class Codec:
                        "hom_add_multi")
         return out, size
 
+    def decompress_sum(self, streams, n: int, eb: float, out=None, stream_bytes=None):
+        """Decode up to 8 streams of the same ``n`` values and add them in the quantised domain with
+        one kernel: the values ``decompress(hom_add(... hom_add(s0, s1) ...))`` would give."""
+        import ctypes as C
+
+        k = len(streams)
+        if out is None:
+            out = torch.empty(n, dtype=torch.float32, device=self.device)
+        self._check_f32(out)
+        sp = (C.c_void_p * k)(*[s.data_ptr() for s in streams])
+        nb = (C.c_size_t * k)(*[(s.numel() if stream_bytes is None else int(stream_bytes[i]))
+                                for i, s in enumerate(streams)])
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.hc_decompress_sum(self._h, k, sp, nb, n, eb, out.data_ptr(), _stream_ptr()),
+                       "decompress_sum")
+        return out
+
     def quant_pred(self, x: torch.Tensor, eb: float, mode="outlier", out=None):
         self._check_f32(x)
         n = x.numel()

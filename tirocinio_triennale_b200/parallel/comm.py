@@ -191,11 +191,19 @@ class CompressedAllreduce:
             return int(self.lib.hc_comm_status_site(self._h))
 
     def set_algorithm(self, algorithm: str):
-        """``"ring"``: one fused kernel per reduce-scatter hop (world + 1 launches, the reference's
-        algorithm); ``"direct"``: scatter, reduce, gather in three launches (default).  Same bits."""
-        code = {"ring": 0, "direct": 1}[algorithm]
+        """``"ring"``: one fused kernel per hop, world + 1 launches (the reference's
+        algorithm); ``"direct"``: scatter, reduce, gather in three launches (default); ``"onestep"``:
+        every rank broadcasts its whole compressed message and decodes the sum of all streams, two
+        launches, for messages of at most ``max_count / world`` values (larger ones go direct).
+        Same bits in all three."""
+        code = {"ring": 0, "direct": 1, "onestep": 2}[algorithm]
         _lib.check(self.lib.hc_comm_set_algorithm(self._h, code), "set_algorithm")
         self.algorithm = algorithm
+
+    def set_small_count(self, count: int):
+        """Direct algorithm: messages of at most ``count`` values (and at most ``max_count / world``)
+        take the one-step form (0: never)."""
+        _lib.check(self.lib.hc_comm_set_small_count(self._h, int(count)), "set_small_count")
 
     def set_overlap(self, on: bool = True):
         """Direct algorithm: let steps 2 and 3 start while their predecessor drains (programmatic
