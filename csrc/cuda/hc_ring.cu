@@ -82,6 +82,7 @@ struct hc_comm {
   uint32_t raw_call = 0;
   int algorithm = 1;              // 0 ring (P + 1 kernels), 1 direct (3 kernels), 2 one step (2 kernels) where it fits
   size_t small_count = 0;         // direct: messages of at most this many values take the one-step form
+  int last_form = 1;              // the form the last hc_allreduce took (0 ring, 1 direct, 2 one step)
   bool trace = false;             // record one CUDA event per step of hc_allreduce
   bool overlap = true;            // direct algorithm: steps 2 and 3 start while their predecessor drains
   int share_scatter = 0, share_reduce = 0;  // direct algorithm: quarters of the GPU for steps 1 and 2 (0: all of it)
@@ -140,6 +141,9 @@ int hc_comm_create(hc_comm** out, int rank, int world, size_t max_count, void* c
   c->world = world;
   c->max_count = max_count;
   c->lay = Layout(world, max_count);
+  // Where the one-step form stops paying (values per message; measured on B200 + NVSwitch at 2 and 4
+  // ranks, 64 MiB / 4 Mi values being the largest sizes tried; above 4 ranks a guess on the safe side)
+  c->small_count = world == 2 ? (size_t)12 << 20 : world <= 4 ? (size_t)3 << 19 : (size_t)1 << 19;
   for (int r = 0; r < world; ++r) {
     if (!peer_bases[r] || (reinterpret_cast<uintptr_t>(peer_bases[r]) & 15u)) {
       delete c;
@@ -540,6 +544,8 @@ static int allreduce_onestep(hc_comm* c, const float* d_sbuf, float* d_rbuf, siz
 // Largest count the one-step form can take: what one stream slot holds.
 static size_t onestep_capacity(const hc_comm* c) { return c->lay.slot_elems; }
 
+extern "C" int hc_comm_last_form(hc_comm* c) { return c ? c->last_form : -1; }
+
 extern "C" int hc_comm_set_small_count(hc_comm* c, size_t count) {
   if (!c) return hc::kErrArgument;
   c->small_count = count;
@@ -611,10 +617,13 @@ extern "C" int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size
   if (!c || !d_sbuf || !d_rbuf || !(eb > 0.0f) || count > c->max_count) return hc::kErrArgument;
   if (count == 0) return hc::kOk;
   NvtxRange call_range("hc_allreduce");
+  c->last_form = c->algorithm == 0 ? 0 : 1;
   if (c->algorithm == 0) return allreduce_ring(c, d_sbuf, d_rbuf, count, eb, stream);
   // one step for every message that fits (algorithm 2), or for those up to the small-message limit
-  if (c->world > 1 && count <= onestep_capacity(c) && (c->algorithm == 2 || count <= c->small_count))
+  if (c->world > 1 && count <= onestep_capacity(c) && (c->algorithm == 2 || count <= c->small_count)) {
+    c->last_form = 2;
     return allreduce_onestep(c, d_sbuf, d_rbuf, count, eb, stream);
+  }
   return allreduce_direct(c, d_sbuf, d_rbuf, count, eb, stream);
 }
 

@@ -155,9 +155,13 @@ int hc_allreduce_host(hc_comm* c, const float* h_sbuf, float* h_rbuf, size_t cou
 // take the direct form): every rank broadcasts its whole compressed message and decodes the sum of
 // all streams.  Same result bits again; world - 1 messages on the wire instead of 2 (world - 1) / world.
 int hc_comm_set_algorithm(hc_comm* c, int algorithm);
-// Direct algorithm: messages of at most `count` values (and at most max_count / world) take the
-// one-step form, which has one network phase less (default 0: never).
+// Direct algorithm: messages of at most `count` values that fit one stream slot (max_count / world
+// values; max_count with two ranks) take the one-step form, which has one network phase less.
+// Default: 12 Mi values with 2 ranks, 1.5 Mi with 3 or 4, 512 Ki above; 0: never.
 int hc_comm_set_small_count(hc_comm* c, size_t count);
+// The form the last hc_allreduce took: 0 ring, 1 direct, 2 one step.  hc_comm_last_stream_bytes reports
+// one stream per step of that form (one step: the whole message's stream in word 0, zeros behind it).
+int hc_comm_last_form(hc_comm* c);
 // Direct algorithm: launch steps 2 and 3 with programmatic stream serialisation, so that each fills
 // the SMs while its predecessor drains (default on; off while tracing).  Same results either way.
 int hc_comm_set_overlap(hc_comm* c, int on);

@@ -16,6 +16,7 @@ def _worker(rank, world, counts, eb, algorithm="direct"):
     from tirocinio_triennale_b200.parallel import CompressedAllreduce
 
     ar = CompressedAllreduce(max(counts), timeout_ms=5000, algorithm=algorithm)
+    ar.set_small_count(0)  # the direct form at every size here; the one-step form has a test of its own
     for it, n in enumerate(counts):
         gen = smooth if it % 2 == 0 else gradient_like
         bufs = [gen(n, seed=100 * it + r) for r in range(world)]

@@ -34,6 +34,7 @@ def declare(lib):
         "hc_comm_set_trace": [vp, i],
         "hc_comm_set_algorithm": [vp, i],
         "hc_comm_set_small_count": [vp, sz],
+        "hc_comm_last_form": [vp],
         "hc_comm_set_overlap": [vp, i],
         "hc_comm_set_shares": [vp, i, i, i],
         "hc_comm_set_sparse_tiles": [vp, i],

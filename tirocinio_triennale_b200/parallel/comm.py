@@ -201,8 +201,9 @@ class CompressedAllreduce:
         self.algorithm = algorithm
 
     def set_small_count(self, count: int):
-        """Direct algorithm: messages of at most ``count`` values (and at most ``max_count / world``)
-        take the one-step form (0: never)."""
+        """Direct algorithm: messages of at most ``count`` values that fit one stream slot
+        (``max_count / world`` values; ``max_count`` with two ranks) take the one-step form (0: never;
+        default 12 Mi values with 2 ranks, 1.5 Mi with 3 or 4, 512 Ki above)."""
         _lib.check(self.lib.hc_comm_set_small_count(self._h, int(count)), "set_small_count")
 
     def set_overlap(self, on: bool = True):
@@ -247,8 +248,11 @@ class CompressedAllreduce:
         n, eb = getattr(self, "_last", (0, 0.0))
         sizes = self.last_stream_bytes() if n else []
         produced = [s for s in sizes if s > 0]
-        chunk_bytes = 4.0 * n / self.world
+        form = ("ring", "direct", "onestep")[int(self.lib.hc_comm_last_form(self._h))]
+        # the one-step form produces one stream of the whole message, the others one per chunk
+        chunk_bytes = 4.0 * n if form == "onestep" else 4.0 * n / self.world
         return {
+            "form": form,
             "world": self.world, "rank": self.rank, "algorithm": self.algorithm, "transport": self.transport,
             "multicast": self.multicast, "count": n, "error_bound": eb, "stream_bytes": sizes,
             "compression_ratio": (chunk_bytes * len(produced) / sum(produced)) if produced else None,

@@ -1,7 +1,8 @@
 """Message-size sweep of the compressed allreduce: 4 KB - 1 GB (powers of two) on the smooth
 sinusoid field, error bounds 1e-3 and 1e-5; effective GB/s (message bytes / device time, max over
 ranks), compression ratio, NCCL uncompressed time, and the fraction of the roofline
-max(HBM bytes / measured copy bandwidth, NVLink bytes / 770 GB/s).
+max(HBM bytes / measured copy bandwidth, NVLink bytes / 770 GB/s); `form` says which form of the
+allreduce a size took (small messages take the one-step form unless `--small-count 0`).
 
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
         -m tirocinio_triennale_b200.utils.sweep_allreduce --max-mb 1024 --out sweep8.jsonl
@@ -26,7 +27,9 @@ def main(argv=None):
     ap.add_argument("--max-mb", type=int, default=1024)
     ap.add_argument("--ebs", type=float, nargs="+", default=[1e-3, 1e-5])
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--algorithm", default="direct", choices=["direct", "ring"])
+    ap.add_argument("--algorithm", default="direct", choices=["direct", "ring", "onestep"])
+    ap.add_argument("--small-count", type=int, default=None,
+                    help="direct: values up to which a message takes the one-step form (0: never; default: the library's)")
     ap.add_argument("--out", default=None)
     a = ap.parse_args(argv)
     rank = int(os.environ.get("RANK", "0"))
@@ -41,6 +44,8 @@ def main(argv=None):
     peaks = timing.measured_peaks()
     max_n = a.max_mb * 1024 * 1024 // 4
     ar = CompressedAllreduce(max_n, algorithm=a.algorithm)
+    if a.small_count is not None:
+        ar.set_small_count(a.small_count)
     full = datagen.sinusoid_field(max_n, seed=rank, device="cuda")
     out = torch.empty_like(full)
     flush = timing.L2Flusher()
@@ -72,18 +77,22 @@ def main(argv=None):
         nccl_ms = timed(lambda: dist.all_reduce(ncc))
         for eb in a.ebs:
             ms = timed(lambda: ar.allreduce(x, y, eb))
-            sizes = ar.last_stream_bytes()
-            cr = (4 * n / world) / max(1.0, sum(sizes) / len(sizes))
+            st = ar.stats()
+            cr = st["compression_ratio"] or 1.0
             exact = x.double()
             dist.all_reduce(exact)
             err = float((y.double() - exact).abs().max())
             # bytes this rank's kernels must move: read input, write result, streams in and out
             comp = 4 * n / cr
-            hbm = 4 * n + 4 * n + 4 * comp * (world - 1) / max(world, 1) + 2 * comp
-            link = 2 * comp * (world - 1) / max(world, 1)
+            if st["form"] == "onestep":  # the whole stream to every rank, every rank's stream read once
+                hbm = 4 * n + 4 * n + comp * (1 + world)
+                link = comp * (world - 1)
+            else:
+                hbm = 4 * n + 4 * n + 4 * comp * (world - 1) / max(world, 1) + 2 * comp
+                link = 2 * comp * (world - 1) / max(world, 1)
             roof_ms = max(hbm / (peaks["hbm_gbs"] * 1e9), link / (NVLINK_GBS * 1e9)) * 1e3
             rows.append({"bytes": nbytes, "eb": eb, "world": world, "ms": ms, "effective_GBps": nbytes / ms / 1e6,
-                         "nccl_ms": nccl_ms, "speedup_vs_nccl": nccl_ms / ms, "compression_ratio": cr,
+                         "nccl_ms": nccl_ms, "speedup_vs_nccl": nccl_ms / ms, "compression_ratio": cr, "form": st["form"],
                          "max_abs_err": err, "err_bound": world * eb, "roofline_ms": roof_ms,
                          "roofline_fraction_of_%s" % peaks["source"]: roof_ms / ms, "status": ar.status()})
             if rank == 0:
