@@ -47,9 +47,10 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--ops", default="compress,decompress,hom_add,doc",
-                    help="comma list of compress,decompress,hom_add,doc,scatter7,reduce7 (the last two: the shapes "
-                         "of an 8-rank allreduce on one GPU: 7-segment compress of 7/8 of the data, 7 streams (+) "
-                         "fp32 of 1/8 of it)")
+                    help="comma list of compress,decompress,hom_add,doc,scatter7,reduce7,sum4 (scatter7, reduce7: the "
+                         "shapes of an 8-rank allreduce on one GPU: 7-segment compress of 7/8 of the data, 7 streams "
+                         "(+) fp32 of 1/8 of it; sum4: four streams of a quarter of the data decoded and summed by "
+                         "one kernel, step 2 of the one-step allreduce at 4 ranks)")
     args = ap.parse_args(argv)
 
     x = make_data(args)
@@ -102,6 +103,14 @@ def main(argv=None):
             nb = [int(v) for v in sizes.tolist()]
             report("reduce7", lambda: codec.hom_add_multi(outs, x[:chunk], eb, args.mode, stream_bytes=nb),
                    4 * chunk + 8 * nbytes // 8)
+    if "sum4" in want:
+        # what a rank of 4 does in step 2 of the one-step allreduce, without the peers: four streams of
+        # n / 4 values decoded and summed by one kernel
+        part = n // 4 // 4096 * 4096
+        outs, sizes = codec.compress_batch([x[k * part: (k + 1) * part] for k in range(4)], eb, args.mode)
+        nb = [int(v) for v in sizes.tolist()]
+        dst = torch.empty(part, dtype=torch.float32, device="cuda")
+        report("sum4", lambda: codec.decompress_sum(outs, part, eb, out=dst, stream_bytes=nb), 4 * part + sum(nb))
     res["status"] = codec.status()
     print(json.dumps(res))
     return res
