@@ -266,6 +266,20 @@ static int allreduce_ring(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t
   auto mark = [&]() {
     if (c->trace) cudaEventRecord(c->ev[c->n_ev++], stream);
   };
+  // Every hop consumes only what arrival flags announce and each launch has a workspace set of its own
+  // (epoch % kMaxWorkspaceSets), so a hop may fill the SMs while the hop before it drains, as in the
+  // direct form.  At most kMaxWorkspaceSets kernels may be in flight together, hence a normal launch
+  // (which waits for everything before it) after every kMaxWorkspaceSets - 1 overlapped ones; the first
+  // launch of a call is always a normal one, which the reuse of slots and flags across calls needs.
+  const bool overlap = c->overlap && !c->trace;
+  int chain = 0;
+  bool launched = false;
+  auto overlapped = [&]() -> bool {
+    const bool yes = overlap && launched && chain < hc::kMaxWorkspaceSets - 1;
+    chain = yes ? chain + 1 : 0;
+    launched = true;
+    return yes;
+  };
   mark();
   // ---- reduce-scatter: steps 0 .. P-1 (the last one feeds the all-gather buffers) --------------
   for (int s = 0; s < P; ++s) {
@@ -307,7 +321,8 @@ static int allreduce_ring(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t
     }
     p.sparse = c->sparse ? 1u : 0u;
     p.ws = next_ws(c, stream);
-    if (hc::launch_encode(s == 0 ? hc::kOpCompress : hc::kOpAddF32, hc::kModeOutlier, p, stream) != cudaSuccess)
+    if (hc::launch_encode(s == 0 ? hc::kOpCompress : hc::kOpAddF32, hc::kModeOutlier, p, stream, overlapped()) !=
+        cudaSuccess)
       return hc::kErrCuda;
     mark();
   }
@@ -332,7 +347,7 @@ static int allreduce_ring(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t
     sg.n = n;
   }
   d.ws = next_ws(c, stream);
-  if (hc::launch_decode(hc::kModeOutlier, d, stream) != cudaSuccess) return hc::kErrCuda;
+  if (hc::launch_decode(hc::kModeOutlier, d, stream, overlapped()) != cudaSuccess) return hc::kErrCuda;
   mark();
   return hc::kOk;
 }
