@@ -34,7 +34,7 @@ def build(force: bool = False) -> Path | None:
     src, inc = OUT / "src", OUT / "include"
     src.mkdir(parents=True, exist_ok=True)
     inc.mkdir(parents=True, exist_ok=True)
-    for f in ("GSZ.cu", "homcomp.cu", "GSZ_entry.cu", "cuda_awareallreduce.cu"):
+    for f in ("GSZ.cu", "homcomp.cu", "GSZ_entry.cu", "cuda_awareallreduce.cu", "nca_allreduce.cu"):
         shutil.copyfile(REF / "src" / f, src / f)
     for f in (REF / "include").iterdir():
         shutil.copyfile(f, inc / f.name)
@@ -64,7 +64,7 @@ def build(force: bool = False) -> Path | None:
     cmd = [nvcc, "-std=c++17", "-gencode", "arch=compute_100,code=sm_100", "-O3", "-shared", "-Xcompiler", "-fPIC",
            "-w", "-I", str(SHIM), "-I", str(inc),
            str(src / "GSZ.cu"), str(src / "homcomp.cu"), str(src / "GSZ_entry.cu"), str(src / "cuda_awareallreduce.cu"),
-           str(HERE / "ref_driver.cu"), str(SHIM / "mpi_shim.cpp"), "-o", str(LIB), "-lcudart", "-lrt"]
+           str(src / "nca_allreduce.cu"), str(HERE / "ref_driver.cu"), str(SHIM / "mpi_shim.cpp"), "-o", str(LIB), "-lcudart", "-lrt"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         (OUT / "build.log").write_text(r.stdout + r.stderr)

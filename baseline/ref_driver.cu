@@ -1,5 +1,5 @@
 // extern "C" doorway into the reference library for the Python benchmark arm: it only forwards to
-// the reference's own public functions (HomComp/include/GSZ_entry.h, cuda_awareallreduce.cuh).
+// the reference's own public functions (HomComp/include/GSZ_entry.h, cuda_awareallreduce.cuh, nca_allreduce.cuh).
 #include <cuda_runtime.h>
 #include <mpi.h>
 #include <stddef.h>
@@ -8,6 +8,7 @@
 #include "GSZ_entry.h"
 #include "cuda_awareallreduce.cuh"
 #include "homcomp.cuh"
+#include "nca_allreduce.cuh"
 
 extern "C" {
 
@@ -25,6 +26,11 @@ int ref_allreduce_F(const float* d_sbuf, float* d_rbuf, size_t count, float eb) 
 }
 int ref_allreduce_F_opt(const float* d_sbuf, float* d_rbuf, size_t count, float eb) {
   return allreduce_ring_comprs_hom_sum_F_opt(d_sbuf, d_rbuf, count, MPI_COMM_WORLD, eb);
+}
+// the reference's variant for GPUs that cannot address each other: compressed chunks through host
+// memory and MPI (HomComp/src/nca_allreduce.cu:195-324)
+int ref_allreduce_cpucopy_F(const float* d_sbuf, float* d_rbuf, size_t count, float eb) {
+  return cpuCopy_allreduce_ring_comprs_hom_sum_F(d_sbuf, d_rbuf, count, MPI_COMM_WORLD, eb);
 }
 int ref_allreduce_gpu(const float* d_sbuf, float* d_rbuf, size_t count) {
   return allreduce_ring_gpu(d_sbuf, d_rbuf, count, MPI_COMM_WORLD);

@@ -46,6 +46,9 @@ def _load():
     lib.ref_barrier.restype = C.c_int
     lib.ref_allreduce_F.restype = C.c_int
     lib.ref_allreduce_F.argtypes = [vp, vp, sz, f]
+    if hasattr(lib, "ref_allreduce_cpucopy_F"):
+        lib.ref_allreduce_cpucopy_F.restype = C.c_int
+        lib.ref_allreduce_cpucopy_F.argtypes = [vp, vp, sz, f]
     lib.ref_compress.restype = sz
     lib.ref_compress.argtypes = [vp, vp, sz, f]
     lib.ref_decompress.restype = None
