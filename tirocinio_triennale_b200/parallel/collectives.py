@@ -45,6 +45,16 @@ def _host_group(group):
 
 
 _codecs = {}
+_bounces = {}
+
+
+def _bounce_for(device, nbytes):
+    """Pinned host buffer for the device -> host leg, kept between calls: pinning tens of megabytes
+    costs milliseconds, more than the copies it serves."""
+    key = str(device)
+    if key not in _bounces or _bounces[key].numel() < nbytes:
+        _bounces[key] = torch.empty(int(nbytes), dtype=torch.uint8).pin_memory()
+    return _bounces[key]
 
 
 def _codec_for(device, max_elems):
@@ -74,7 +84,7 @@ def cpuCopy_allreduce_ring_comprs_hom_sum_F(d_sbuf: torch.Tensor, d_rbuf: torch.
     src = d_sbuf.reshape(-1)
     dst = d_rbuf.reshape(-1)
     cap = ops.max_compressed_bytes(B) + 64
-    bounce = torch.empty(cap, dtype=torch.uint8).pin_memory()
+    bounce = _bounce_for(dev, cap)
 
     def chunk(c):
         return src[c * B: min((c + 1) * B, n)]
