@@ -1,6 +1,6 @@
 """Per-CTA timeline of the codec kernels (instrumented build, ``-DHC_TIMELINE``).
 
-    HC_TIMELINE=1 python -m tirocinio_triennale_b200.utils.timeline --n 16777216 --ops compress,decompress,hom_add
+    HC_TIMELINE=1 python -m tirocinio_triennale_b200.utils.timeline --n 16777216 --ops compress,decompress,hom_add,reduce7
 
 The instrumented library (``_build.build_cuda(timeline=True)`` -> ``libhomcomp_b200_tl.so``) makes
 every CTA write, for the last four launches, nanosecond stamps of its first tile's way through the
@@ -83,6 +83,7 @@ def main():
     size2 = torch.zeros_like(size)
     flush = torch.empty(64 * 1024 * 1024, dtype=torch.int32, device="cuda")
     read(lib)
+    parts = None
     for op in args.ops.split(","):
         for rep in range(args.reps):
             flush.add_(1)
@@ -95,6 +96,15 @@ def main():
                 phases = DECODE_PHASES
             elif op == "hom_add":
                 codec.hom_add(stream, y, args.eb, out=out, size=size2, stream_bytes=nbytes)
+                phases = ENCODE_PHASES
+            elif op == "reduce7":
+                # the reduce step of an 8-rank allreduce on one GPU: 7 streams (+) fp32 of n / 8 values
+                if parts is None:
+                    chunk = n // 8 // 4096 * 4096
+                    parts = codec.compress_batch([x[(k + 1) * chunk: (k + 2) * chunk] for k in range(7)], args.eb)
+                    part_bytes = [int(v) for v in parts[1].tolist()]
+                    read(lib)
+                codec.hom_add_multi(parts[0], y[:chunk], args.eb, stream_bytes=part_bytes)
                 phases = ENCODE_PHASES
             else:
                 raise SystemExit("unknown op " + op)
