@@ -76,8 +76,9 @@ def _missing_peer(rank, world):
     want = ops.cpu_ring_allreduce(bufs, eb)[rank]
     x = torch.from_numpy(bufs[rank]).cuda()
     out = torch.empty_like(x)
-    for algorithm in ("direct", "ring"):
+    for algorithm in ("direct", "onestep", "ring"):
         ar.set_algorithm(algorithm)
+        ar.set_small_count(0)  # "direct" means the three-step form here, whatever the size
         ar.allreduce(x, out, eb)
         assert ar.status() == 0
         np.testing.assert_array_equal(out.cpu().numpy(), want)
