@@ -35,6 +35,10 @@ def main(argv=None):
     ap.add_argument("--count", type=int, default=16 * 1024 * 1024)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--algorithm", default="direct", choices=["direct", "ring", "onestep"])
+    ap.add_argument("--trace", action="store_true",
+                    help="afterwards: device time of every step of the collective (CUDA events between the launches, "
+                         "which also serialises the steps), median over --iter calls, maximum over ranks")
     a = ap.parse_args(argv)
 
     rank = int(os.environ.get("RANK", "0"))
@@ -54,7 +58,7 @@ def main(argv=None):
         x = datagen.from_distribution(a.count, a.data, 0, "cuda")
     n = x.numel()
     out = torch.empty_like(x)
-    ar = CompressedAllreduce(n)
+    ar = CompressedAllreduce(n, algorithm=a.algorithm)
 
     def call():
         if a.mode == "mixed":
@@ -93,6 +97,20 @@ def main(argv=None):
         y = x.clone()
         lo, hi, avg = bench(lambda: dist.all_reduce(y))
         res["nccl_s"] = {"min": lo, "max": hi, "avg": avg}
+    if a.trace and a.mode not in ("mixed", "raw"):
+        ar.set_trace(True)
+        steps = []
+        for it in range(a.iter + a.warmup):
+            dist.barrier()
+            ar.allreduce(x, out, a.eb)
+            ms = ar.last_step_ms()
+            if it >= a.warmup:
+                steps.append(ms)
+        ar.set_trace(False)
+        med = torch.tensor(np.median(np.array(steps), axis=0), dtype=torch.float64, device="cuda")
+        dist.all_reduce(med, op=dist.ReduceOp.MAX)
+        res["form"] = ar.stats()["form"]
+        res["step_ms"] = [round(float(v), 4) for v in med]
     if rank == 0:
         print(json.dumps(res), flush=True)
         if a.out:
