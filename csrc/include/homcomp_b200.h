@@ -138,8 +138,9 @@ int hc_comm_set_timeout_ms(hc_comm* c, unsigned ms);
 int hc_comm_status(hc_comm* c, int clear);  // synchronises; sticky hc::Status of all the handle's kernels
 int hc_comm_status_site(hc_comm* c);        // after a time-out: the wait that ran out first (see hc_codec_status_site)
 // Sum of `count` floats over all ranks, error at most world * eb per value; d_sbuf and d_rbuf may
-// alias.  Enqueues 3 kernels (direct algorithm, the default) or world + 1 (ring) on `stream`; never
-// allocates or synchronises.
+// alias.  Enqueues 3 kernels (direct algorithm, the default; 2 for the small messages that take its
+// one-step form, see hc_comm_set_small_count) or world + 1 (ring) on `stream`; never allocates or
+// synchronises.
 int hc_allreduce(hc_comm* c, const float* d_sbuf, float* d_rbuf, size_t count, float eb, hc_stream_t stream);
 // The same sum for buffers in (pinned) host memory: the message crosses PCIe in `pieces` pieces
 // (0 = default: pieces of 4 MiB, at most 16; never more than 32) on two copy streams of the handle while earlier pieces are reduced on

@@ -17,8 +17,8 @@ from .. import _lib
 class CompressedAllreduce:
     """Handle-based compressed allreduce for float32 CUDA tensors of up to ``max_count`` values.
 
-    Every call enqueues 3 kernels (``"direct"``, the default) or ``world + 1`` (``"ring"``) on the
-    current stream: it never allocates, never synchronises the host and never copies a size to the host.  The result is identical on all
+    Every call enqueues 3 kernels (``"direct"``, the default; 2 for the small messages that take its
+    one-step form, see ``set_small_count``) or ``world + 1`` (``"ring"``) on the current stream: it never allocates, never synchronises the host and never copies a size to the host.  The result is identical on all
     ranks and equals ``2 * eb * sum_r quantise(x_r)``: the error is at most ``world * eb``.
     """
 
